@@ -367,10 +367,17 @@ int mtx_engine_rebind_state(mtx_engine* e, const mtx_decode_state* s);
 
 #define MTX_NORM_OUT_GAIN 0 /* x += gain * unit(sub(x)): the sublayer reads x itself, one gain on its output */
 #define MTX_NORM_SANDWICH 1 /* x += wnorm(sub(wnorm(x, pre)), post) with wnorm(y, w) = unit(y) * (1 + w), weights [width] */
+#define MTX_NORM_PARALLEL 2 /* ONE norm per layer, both sublayers read it: h = gnorm(x, norm1), the row cut into
+                               mtx_layered_config.norm_groups consecutive parts that are each brought to unit RMS, times the weight as
+                               stored;  x += residual_mult * (mixer(h + conv1(h)) + ff(h + conv2(h))), where conv is a causal
+                               convolution over time on each channel (conv_taps taps, zeros before the sequence's start; the last
+                               conv_taps - 1 rows of h are state of the sequence).  Mixer and feed-forward share ONE output projection
+                               over their concatenated activations */
 
 #define MTX_FF_GELU_GATED 0    /* down(gelu_tanh(gate x) * up x) */
 #define MTX_FF_CLAMPED_GATED 1 /* down(g s(1.702 g) (u + 1)), g = min(gate x, limit), u = clamp(up x, -limit, limit), s = sigmoid */
 #define MTX_FF_MOE 2           /* routed experts of the clamped form plus an optional shared one (mtx_moe_desc) */
+#define MTX_FF_RELU2 3         /* down(relu(up x)^2); MTX_NORM_PARALLEL layers: w_gate_up = up [ff, width], down is part of wo */
 
 /* Causal softmax attention over the paged cache (csrc/softmax_attention.cuh).  Its projection rows in the layer's w_in are
  * [q: heads*dim | k: kv_heads*dim | v: kv_heads*vdim unless values_are_keys]. */
@@ -386,11 +393,46 @@ typedef struct {
   const double* rot_freq;  /* [rot_dims / 2] radians per position of pair i */
   void* k_pages;           /* [kv_heads, num_pages, tokens_per_page, dim] */
   void* v_pages;           /* [kv_heads, num_pages, tokens_per_page, vdim] */
+  /* -- optional parts (all zero / NULL: the attention described above) -- */
+  int32_t rot_half;        /* 1: channel i < rot_dims / 2 is paired with channel i + rot_dims / 2 instead of (2i, 2i + 1) */
+  int32_t shared_kv;       /* 1: the layer has no key / value projections; k_pages / v_pages are the pools of an earlier layer with the
+                              same head geometry, read as that layer wrote them (keys after its norm and rotation) */
+  int32_t head_gate;       /* 1: `heads` more projection rows follow the attention's own: head h's output is multiplied by
+                              sigmoid(row h) */
+  const float* q_norm;     /* [dim] or NULL: every query head is brought to unit RMS (the layer's eps) and multiplied by this */
+  const float* k_norm;     /* [dim] or NULL: the same for the key heads, before they are cached */
+  const float* slopes;     /* [heads] or NULL: slopes[h] * (i - j) is taken off the scaled score of key j for the query at i */
+  const float* sink;       /* [heads] or NULL: exp(sink[h]) is added to the softmax's denominator (no key, no value, not scaled) */
 } mtx_softmax_attn_desc;
+
+/* Attention through latents (csrc/latent_attention.cuh): queries q = w_uq rmsnorm(dq x) laid out per head as [dim plain | rot_dim
+ * rotated]; the cache holds, per token, the normed latent c = rmsnorm((dkv x)[:kv_rank]) and ONE rotated key part shared by all
+ * heads (the last rot_dim rows of dkv x); head h's plain key is w_uk_h c and its value w_uv_h c.  Served as one-key-head attention
+ * in the latent space: the plain query is taken through w_uk_h^T, so that score = scale * (<q_lat, c> + <q_rot, k_rot>), the
+ * weighted sum runs over the cached rows themselves and w_uv_h expands the result.  Projection rows in w_in: [dq: q_rank |
+ * dkv: kv_rank + rot_dim | head gates: heads]. */
+typedef struct {
+  int32_t heads;           /* 0: the layer has no latent attention */
+  int32_t dim, rot_dim, vdim, q_rank, kv_rank;
+  int32_t rot_half;        /* pairing of the rotated channels, as in mtx_softmax_attn_desc */
+  float scale;
+  const double* rot_freq;  /* [rot_dim / 2] */
+  const float* q_norm;     /* [q_rank] */
+  const float* kv_norm;    /* [kv_rank] */
+  const float* sink;       /* [heads] or NULL */
+  const void* w_uq;        /* [heads * (dim + rot_dim), q_rank] */
+  const void* w_uk_t;      /* [heads, kv_rank, dim]: per head, the key expansion transposed */
+  const void* w_uv;        /* [heads, vdim, kv_rank] */
+  void* pages;             /* [1, num_pages, tokens_per_page, kv_rank + rot_dim] */
+} mtx_latent_attn_desc;
 
 #define MTX_REC_GLA 1   /* S = diag(a) S + k v^T, o = S^T q, a = sigmoid(z)^(1 / tau) per key channel, z = low-rank projection */
 #define MTX_REC_MLSTM 2 /* S = e^(f + m' - m) S + e^(i - m) k v^T, n likewise with k alone, m = max(f + m', i) from m = 0;
                            o = S^T q / (max(|n.q|, e^-m) + denom_eps); i = cap tanh(./cap), f = logsigmoid(cap tanh(./cap)) */
+#define MTX_REC_DELTA 3 /* S = diag(w) S' - (a u)(u^T S') + k v^T (both first terms read the old state S'), o = S^T q;
+                           u = k / sqrt(|k|^2 + key_eps) per head; w = exp(-decay_rate sigmoid(z)) per key channel with
+                           z = up tanh(down x) + decay_bias; a = sigmoid(a x + gate_bias) per key channel.  Projection rows:
+                           [q | k | v | output gate: heads*vdim | a: heads*dim | decay_rank rows of the decay's down-projection] */
 
 /* A linear recurrence with a matrix state per head (csrc/recurrent_mixers.cuh).  State, decays and gates are fp32.  Its
  * projection rows in w_in follow the attention's: [q: heads*dim | k: heads*dim | v: heads*vdim | output gate: heads*vdim |
@@ -412,6 +454,8 @@ typedef struct {
   float* state_s;          /* [state slots, heads, vdim, dim] (a value column's key channels are contiguous) */
   float* state_n;          /* mLSTM: [state slots, heads, dim] */
   float* state_m;          /* mLSTM: [state slots, heads] */
+  float decay_rate;        /* MTX_REC_DELTA */
+  float key_eps;           /* MTX_REC_DELTA */
 } mtx_recurrent_desc;
 
 /* Routed feed-forward (csrc/moe.cuh): scores s = sigmoid(router x); an expert is chosen by s + correction among the experts of
@@ -473,6 +517,13 @@ typedef struct {
   mtx_softmax_attn_desc attn;
   mtx_recurrent_desc rec;
   mtx_moe_desc moe;
+  /* -- MTX_NORM_PARALLEL layers -- */
+  mtx_latent_attn_desc latent;
+  int32_t conv_taps;       /* taps of the input convolutions; 0 or 1 with NULL weights: none */
+  float residual_mult;
+  const float* conv1;      /* [conv_taps, width] (tap-major: tap j multiplies the row conv_taps - 1 - j steps back), mixer input */
+  const float* conv2;      /* the same for the feed-forward's input, or NULL */
+  float* conv_state;       /* [state slots, conv_taps - 1, width]: the normed row of position p is kept at index p % (conv_taps - 1) */
 } mtx_layer_desc;
 
 typedef struct {
@@ -494,6 +545,9 @@ typedef struct {
   const void* head;            /* [vocab, width] */
   const float* final_norm;     /* NULL: the final norm has the single gain final_gain; else weights [width], unit(x) * (1 + w) */
   float logit_softcap;         /* cap * tanh(logits / cap); 0 = off */
+  int32_t norm_groups;         /* MTX_NORM_PARALLEL models: parts of a row that are normed on their own (also in the final norm, whose
+                                  weight is then used as stored); 0 for the other norm styles */
+  float logit_scale;           /* multiplies the logits before the cap; 0 = 1 */
 } mtx_layered_config;
 
 typedef struct {

@@ -109,9 +109,9 @@ class DecodeState(ctypes.Structure):
 
 
 MIXER_WINDOW_SIGMOID, MIXER_COMPOSITE = 1, 2
-NORM_OUT_GAIN, NORM_SANDWICH = 0, 1
-FF_GELU_GATED, FF_CLAMPED_GATED, FF_MOE = 0, 1, 2
-REC_GLA, REC_MLSTM = 1, 2
+NORM_OUT_GAIN, NORM_SANDWICH, NORM_PARALLEL = 0, 1, 2
+FF_GELU_GATED, FF_CLAMPED_GATED, FF_MOE, FF_RELU2 = 0, 1, 2, 3
+REC_GLA, REC_MLSTM, REC_DELTA = 1, 2, 3
 
 
 class SoftmaxAttnDesc(ctypes.Structure):
@@ -121,6 +121,18 @@ class SoftmaxAttnDesc(ctypes.Structure):
       [(n, ctypes.c_int32) for n in ("heads", "kv_heads", "dim", "vdim", "window", "rot_dims", "values_are_keys")]
       + [(n, ctypes.c_float) for n in ("scale", "out_scale")]
       + [(n, ctypes.c_void_p) for n in ("rot_freq", "k_pages", "v_pages")]
+      + [(n, ctypes.c_int32) for n in ("rot_half", "shared_kv", "head_gate")]
+      + [(n, ctypes.c_void_p) for n in ("q_norm", "k_norm", "slopes", "sink")]
+  )
+
+
+class LatentAttnDesc(ctypes.Structure):
+  """mtx_latent_attn_desc."""
+
+  _fields_ = (
+      [(n, ctypes.c_int32) for n in ("heads", "dim", "rot_dim", "vdim", "q_rank", "kv_rank", "rot_half")]
+      + [("scale", ctypes.c_float)]
+      + [(n, ctypes.c_void_p) for n in ("rot_freq", "q_norm", "kv_norm", "sink", "w_uq", "w_uk_t", "w_uv", "pages")]
   )
 
 
@@ -131,6 +143,7 @@ class RecurrentDesc(ctypes.Structure):
       [(n, ctypes.c_int32) for n in ("kind", "heads", "dim", "vdim", "decay_rank", "gate_silu")]
       + [(n, ctypes.c_float) for n in ("q_scale", "tau", "gate_cap", "denom_eps", "out_scale")]
       + [(n, ctypes.c_void_p) for n in ("decay_up_t", "decay_bias", "gate_bias", "out_norm", "state_s", "state_n", "state_m")]
+      + [(n, ctypes.c_float) for n in ("decay_rate", "key_eps")]
   )
 
 
@@ -155,7 +168,9 @@ class LayerDesc(ctypes.Structure):
       + [(n, ctypes.c_int32) for n in ("norm_style", "ff_kind", "n_in", "add_embedding")]
       + [("ff_limit", ctypes.c_float)]
       + [(n, ctypes.c_void_p) for n in ("norm1", "norm1b", "norm2", "norm2b", "add_vector", "w_in", "b_in", "bo")]
-      + [("attn", SoftmaxAttnDesc), ("rec", RecurrentDesc), ("moe", MoeDesc)]
+      + [("attn", SoftmaxAttnDesc), ("rec", RecurrentDesc), ("moe", MoeDesc), ("latent", LatentAttnDesc)]
+      + [("conv_taps", ctypes.c_int32), ("residual_mult", ctypes.c_float)]
+      + [(n, ctypes.c_void_p) for n in ("conv1", "conv2", "conv_state")]
   )
 
 
@@ -167,7 +182,7 @@ class LayeredConfig(ctypes.Structure):
                                      "tokens_per_page", "max_pages_per_group")]
       + [(n, ctypes.c_float) for n in ("eps", "embed_scale", "final_gain")]
       + [(n, ctypes.c_void_p) for n in ("embedding", "head", "final_norm")]
-      + [("logit_softcap", ctypes.c_float)]
+      + [("logit_softcap", ctypes.c_float), ("norm_groups", ctypes.c_int32), ("logit_scale", ctypes.c_float)]
   )
 
 

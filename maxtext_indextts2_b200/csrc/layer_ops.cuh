@@ -9,6 +9,11 @@
 //                           x += wnorm(y + bias, post); x += embedding output; x += vector; xa = wnorm(x, pre)   (each part optional)
 //                           with wnorm(y, w) = y / sqrt(mean(y^2) + eps) * (1 + w)
 //   weighted_norm_rows_kernel  wnorm of a gathered subset of rows;  softcap_kernel  z = cap * tanh(z / cap)
+//   group_norm_step_kernel  x += mult * y (optional); h = gnorm(x) * w (w null: no h), the row normed in `groups` consecutive parts of their own (fp32 out)
+//   input_conv_kernel       per-channel causal convolutions over time on h: a = h + conv1(h), b = h + conv2(h) in the matmul dtype; rows
+//                           before a run's first come from the sequence's state (a ring of the last taps - 1 normed rows)
+//   conv_state_update_kernel  the last rows of every run go into that ring
+//   group_norm_rows_kernel  gnorm of a gathered subset of rows;  logit_post_kernel  z = cap * tanh(scale * z / cap)
 //
 // Everything here is fp32 arithmetic; T is the dtype the matrix products and the cache use (bf16, or float for a float32 engine).
 #pragma once
@@ -171,6 +176,126 @@ __global__ void softcap_kernel(float* z, float cap, long long total) {
   griddep_wait();
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x)
     z[i] = cap * tanhf(z[i] / cap);
+}
+
+// one CTA of eight warps per row.  A group's sum of squares is added in a fixed order: by one warp when there are eight groups or
+// more, else by 8 / groups warps whose partial sums meet in shared memory.
+__global__ void __launch_bounds__(256) group_norm_step_kernel(const float* y, float mult, float* x, const float* w, float eps, float* h, int width,
+                                                              int groups) {
+  __shared__ float red[8];
+  griddep_wait();
+  const int r = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gs = width / groups;
+  float* xr = x + size_t(r) * width;
+  const float* yr = y ? y + size_t(r) * width : nullptr;
+  float* hr = h + size_t(r) * width;
+  if (groups >= 8) {
+    for (int g = warp; g < groups; g += 8) {
+      const int base = g * gs;
+      float ss = 0.0f;
+      for (int c = lane; c < gs; c += 32) {
+        float v = xr[base + c];
+        if (yr) {
+          v = fmaf(mult, yr[base + c], v);
+          xr[base + c] = v;
+        }
+        ss = fmaf(v, v, ss);
+      }
+      ss = warp_sum(ss);
+      const float f = 1.0f / sqrtf(ss / float(gs) + eps);
+      if (w)
+        for (int c = lane; c < gs; c += 32) hr[base + c] = xr[base + c] * f * w[base + c];
+    }
+    return;
+  }
+  const int wpg = 8 / groups, g = warp / wpg, wi = warp % wpg;
+  const bool on = g < groups;
+  const int base = g * gs;
+  float ss = 0.0f;
+  if (on) {
+    for (int c = wi * 32 + lane; c < gs; c += wpg * 32) {
+      float v = xr[base + c];
+      if (yr) {
+        v = fmaf(mult, yr[base + c], v);
+        xr[base + c] = v;
+      }
+      ss = fmaf(v, v, ss);
+    }
+  }
+  ss = warp_sum(ss);
+  if (lane == 0) red[warp] = ss;
+  __syncthreads();
+  if (!on || !w) return;
+  float tot = 0.0f;
+  for (int i = 0; i < wpg; ++i) tot += red[g * wpg + i];
+  const float f = 1.0f / sqrtf(tot / float(gs) + eps);
+  for (int c = wi * 32 + lane; c < gs; c += wpg * 32) hr[base + c] = xr[base + c] * f * w[base + c];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) group_norm_rows_kernel(const float* x, const int* rows, const float* w, float eps, T* out, int width, int groups) {
+  griddep_wait();
+  const int src = rows ? rows[blockIdx.x] : int(blockIdx.x), warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gs = width / groups;
+  const float* xr = x + size_t(src) * width;
+  for (int g = warp; g < groups; g += 8) {  // (only the rows whose logits are wanted come here: a warp per group is enough)
+    const int base = g * gs;
+    float ss = 0.0f;
+    for (int c = lane; c < gs; c += 32) ss = fmaf(xr[base + c], xr[base + c], ss);
+    ss = warp_sum(ss);
+    const float f = 1.0f / sqrtf(ss / float(gs) + eps);
+    for (int c = lane; c < gs; c += 32) out[size_t(blockIdx.x) * width + base + c] = to_act<T>(xr[base + c] * f * w[base + c]);
+  }
+}
+
+__global__ void logit_post_kernel(float* z, float scale, float cap, long long total) {
+  griddep_wait();
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const float v = z[i] * scale;
+    z[i] = cap > 0.0f ? cap * tanhf(v / cap) : v;
+  }
+}
+
+template <typename T>
+struct InputConvArgs {
+  const float* h;        // [rows, width] the normed rows of this step
+  const float* w1;       // [taps, width]: tap j multiplies the row taps - 1 - j steps back (the last tap the row itself)
+  const float* w2;       // the same for the second output, or null
+  const float* state;    // [slots, taps - 1, width]: the normed row of position p of a sequence at index p % (taps - 1)
+  T* out1;               // [rows, width] h + conv1(h)
+  T* out2;               // [rows, width] h + conv2(h) (w2 null: h itself)
+  const int* group;
+  const int* pos;
+  int rows, width, taps;
+};
+
+// one CTA per row.  The row `back` steps before row r is row r - back of the batch when that is the same sequence's previous
+// position (rows of a run are consecutive), a row of the state when the run began later, and zero before the sequence's start.
+template <typename T>
+__global__ void __launch_bounds__(256) input_conv_kernel(const InputConvArgs<T> a) {
+  griddep_wait();
+  const int r = blockIdx.x, W = a.width, p = a.pos[r], grp = a.group[r], ring = a.taps - 1;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    const float own = a.h[size_t(r) * W + c];
+    float s1 = own * a.w1[size_t(ring) * W + c], s2 = a.w2 ? own * a.w2[size_t(ring) * W + c] : 0.0f;
+    for (int back = 1; back <= ring && back <= p; ++back) {
+      const int rr = r - back;
+      const bool in_batch = rr >= 0 && a.group[rr] == grp && a.pos[rr] == p - back;
+      const float v = in_batch ? a.h[size_t(rr) * W + c] : a.state[(size_t(grp) * ring + (p - back) % ring) * W + c];
+      s1 = fmaf(v, a.w1[size_t(ring - back) * W + c], s1);
+      if (a.w2) s2 = fmaf(v, a.w2[size_t(ring - back) * W + c], s2);
+    }
+    a.out1[size_t(r) * W + c] = to_act<T>(own + s1);
+    a.out2[size_t(r) * W + c] = to_act<T>(own + s2);
+  }
+}
+
+// grid (runs, taps - 1): CTA (run, i) keeps the run's i-th row from its end, if the run is that long
+__global__ void __launch_bounds__(256) conv_state_update_kernel(const float* h, float* state, const int* run_row0, const int* group, const int* pos,
+                                                                int width, int taps) {
+  griddep_wait();
+  const int r0 = run_row0[blockIdx.x], r1 = run_row0[blockIdx.x + 1], r = r1 - 1 - int(blockIdx.y), ring = taps - 1;
+  if (r < r0) return;
+  float* dst = state + (size_t(group[r]) * ring + pos[r] % ring) * width;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = h[size_t(r) * width + c];
 }
 
 template <typename T>

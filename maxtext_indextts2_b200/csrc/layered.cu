@@ -2,7 +2,8 @@
 // batches whose keys and values live in page pools.  Host code only: the kernels are in linear_any.cuh (any-shape projections, also
 // grouped by expert), gemm_rows.cuh (the tcgen05 projections, for shapes made of whole 128 x 64 tiles), layer_ops.cuh (norms,
 // residual, cache append), window_attention*.cuh (the sigmoid window mixer), softmax_attention.cuh (causal softmax attention with
-// rotary positions), recurrent_mixers.cuh (GLA and mLSTM over state slots) and moe.cuh (routing).
+// rotary positions), recurrent_mixers.cuh (GLA, mLSTM and the delta rule over state slots), latent_attention.cuh (attention through
+// cached latents) and moe.cuh (routing).
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -16,6 +17,7 @@
 #include "window_attention_decode.cuh"
 #include "softmax_attention.cuh"
 #include "recurrent_mixers.cuh"
+#include "latent_attention.cuh"
 #include "moe.cuh"
 #include "host_util.cuh"
 
@@ -48,6 +50,11 @@ struct mtx_layered {
   float *x0 = nullptr, *rec_o = nullptr, *rec_aux = nullptr, *moe_logits = nullptr, *moe_weight = nullptr, *moe_y = nullptr;
   int *moe_chosen = nullptr, *moe_slot = nullptr, *moe_row = nullptr, *moe_off = nullptr;
   void* moe_act = nullptr;
+  // MTX_NORM_PARALLEL layers: the normed rows (fp32), the feed-forward's input, the latent attention's query and result planes
+  bool parallel = false;
+  int max_lat_q = 0, max_lat_o = 0;
+  float *h = nullptr, *lat_q = nullptr;
+  void *xb = nullptr, *lat_o = nullptr;
 };
 
 namespace {
@@ -57,6 +64,7 @@ size_t elem(const mtx_layered* e) { return e->cfg.float32 ? 4 : 2; }
 struct LWs {
   size_t x, y, qkv, v_shared, xa, q, attn, act, wanted, obf, attn_part, total;
   size_t smax_ml, x0, rec_o, rec_aux, moe_logits, moe_weight, moe_y, moe_chosen, moe_slot, moe_row, moe_off, moe_act;
+  size_t h, xb, lat_q, lat_o;
 };
 
 LWs layered_layout(const mtx_layered* e) {
@@ -94,6 +102,10 @@ LWs layered_layout(const mtx_layered* e) {
   L.moe_row = take((RT + 1) * 4);
   L.moe_off = take(size_t(e->max_moe_experts + 2) * 4);
   L.moe_act = take((RT * size_t(e->max_moe_ff) + 1) * es);
+  L.h = take(e->parallel ? R * c.width * 4 : 4);
+  L.xb = take(e->parallel ? R * c.width * es : 4);
+  L.lat_q = take(R * size_t(e->max_lat_q > 0 ? e->max_lat_q : 1) * 4);
+  L.lat_o = take(R * size_t(e->max_lat_o > 0 ? e->max_lat_o : 1) * es);
   L.total = off;
   return L;
 }
@@ -124,7 +136,7 @@ __global__ void gate_up_bf16_kernel(const bf16* src, bf16* act, int ff, long lon
 // out (fp32, or the gated activation) = EPI(a[rows, k] . w[n, k]^T)
 template <typename T, int EPI>
 int run_linear(mtx_layered* e, const void* a, const void* w, const float* bias, float* out, void* act, int rows, int n, int k, cudaStream_t st,
-               float limit = 0.0f) {
+               float limit = 0.0f, long long ldo = 0) {
   if (rows <= 0) return MTX_OK;
   LinArgs<T> p;
   memset(&p, 0, sizeof(p));
@@ -135,13 +147,26 @@ int run_linear(mtx_layered* e, const void* a, const void* w, const float* bias, 
   p.out = out;
   p.act = static_cast<T*>(act);
   p.lda = k;
-  p.ldo = (EPI == LIN_GATED || EPI == LIN_GATED_CLAMP) ? n / 2 : n;
+  p.ldo = ldo > 0 ? ldo : ((EPI == LIN_GATED || EPI == LIN_GATED_CLAMP) ? n / 2 : n);
   p.rows = rows;
   p.n = n;
   p.k = k;
   const dim3 grid((n + 63) / 64, (rows + 63) / 64);
   if constexpr (sizeof(T) == 4) return launch(linear_f32_kernel<EPI>, grid, dim3(kLinF32Threads), 0, st, p);
   else return launch(linear_mma_kernel<EPI>, grid, dim3(kLinThreads), 0, st, p);
+}
+
+// (relu2: max(., 0)^2; act has the row pitch ldo)
+__global__ void act_bf16_kernel(const bf16* src, bf16* act, int n, long long ldo, long long total, int relu2) {
+  griddep_wait();
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    float v = __bfloat162float(src[i]);
+    if (relu2) {
+      v = fmaxf(v, 0.0f);
+      v *= v;
+    }
+    act[(i / n) * ldo + i % n] = __float2bfloat16_rn(v);
+  }
 }
 
 // the same product on the tcgen05 GEMM: the bf16 result stays in e->obf (256-row blocks)
@@ -161,12 +186,14 @@ int run_umma_raw(mtx_layered* e, const void* a, const void* w, int rows, int n, 
 // ... then the epilogue as a row kernel
 template <int EPI>
 int run_linear_umma(mtx_layered* e, const void* a, const void* w, const float* bias, float* out, void* act, int rows, int n, int k, cudaStream_t st,
-                    float limit = 0.0f) {
+                    float limit = 0.0f, long long ldo = 0) {
   MTX_TRY(run_umma_raw(e, a, w, rows, n, k, st));
   const bf16* tmp = static_cast<const bf16*>(e->obf);
   constexpr bool gated = EPI == LIN_GATED || EPI == LIN_GATED_CLAMP;
   const long long total = (long long)rows * (gated ? n / 2 : n);
   const int blocks = int((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+  if (EPI == LIN_ACT || EPI == LIN_RELU2)
+    return launch(act_bf16_kernel, dim3(blocks), dim3(256), 0, st, tmp, static_cast<bf16*>(act), n, ldo > 0 ? ldo : (long long)n, total, EPI == LIN_RELU2 ? 1 : 0);
   if (gated)
     return launch(gate_up_bf16_kernel, dim3(blocks), dim3(256), 0, st, tmp, static_cast<bf16*>(act), n / 2, total, EPI == LIN_GATED_CLAMP ? limit : 0.0f);
   return launch(bf16_rows_to_f32_kernel, dim3(blocks), dim3(256), 0, st, tmp, bias, out, n, total);
@@ -176,11 +203,36 @@ bool takes_umma(const mtx_layered* e, int rows, int n, int k) { return fits_umma
 
 template <typename T, int EPI>
 int linear(mtx_layered* e, const void* a, const void* w, const float* bias, float* out, void* act, int rows, int n, int k, cudaStream_t st,
-           float limit = 0.0f) {
+           float limit = 0.0f, long long ldo = 0) {
   if constexpr (sizeof(T) == 2) {
-    if (takes_umma(e, rows, n, k)) return run_linear_umma<EPI>(e, a, w, bias, out, act, rows, n, k, st, limit);
+    if (takes_umma(e, rows, n, k)) return run_linear_umma<EPI>(e, a, w, bias, out, act, rows, n, k, st, limit, ldo);
   }
-  return run_linear<T, EPI>(e, a, w, bias, out, act, rows, n, k, st, limit);
+  return run_linear<T, EPI>(e, a, w, bias, out, act, rows, n, k, st, limit, ldo);
+}
+
+// `batches` products over the same rows whose operands lie side by side (linear_any.cuh, batched mode): batch z reads the columns
+// [z * batch_a, z * batch_a + k) of `a`, the weight w + z * w_stride [n, k], and writes the columns [z * batch_o, z * batch_o + n) of
+// `act` in the matmul dtype
+template <typename T>
+int linear_batched(const void* a, long long lda, long long batch_a, const void* w, long long w_stride, void* act, long long ldo, long long batch_o,
+                   int rows, int n, int k, int batches, cudaStream_t st) {
+  if (rows <= 0) return MTX_OK;
+  LinArgs<T> p;
+  memset(&p, 0, sizeof(p));
+  p.a = static_cast<const T*>(a);
+  p.w = static_cast<const T*>(w);
+  p.act = static_cast<T*>(act);
+  p.lda = lda;
+  p.ldo = ldo;
+  p.rows = rows;
+  p.n = n;
+  p.k = k;
+  p.w_group_stride = w_stride;
+  p.batch_a = batch_a;
+  p.batch_o = batch_o;
+  const dim3 grid((n + 63) / 64, (rows + 63) / 64, batches);
+  if constexpr (sizeof(T) == 4) return launch(linear_f32_kernel<LIN_ACT>, grid, dim3(kLinF32Threads), 0, st, p);
+  else return launch(linear_mma_kernel<LIN_ACT>, grid, dim3(kLinThreads), 0, st, p);
 }
 
 // one matrix product per group of slots (linear_any.cuh, grouped mode): slot ranges group_off [groups + 1] on the device, at most
@@ -477,7 +529,7 @@ int launch_rec_scan_t(const RecScanArgs& ra, dim3 grid, dim3 block, size_t smem,
 template <int KIND, int CB, int SL>
 int launch_rec_scan_cb(const RecScanArgs& ra, int n_runs, cudaStream_t st) {
   const dim3 grid(n_runs, ra.heads, (ra.vdim + CB - 1) / CB), block(CB * SL);
-  const size_t smem = rec_scan_smem_bytes(ra.dim, CB, SL, ra.chunk);
+  const size_t smem = rec_scan_smem_bytes(ra.dim, CB, SL, ra.chunk, KIND == REC_DELTA ? 5 : 3);
   const int rpt = rec_rpt(ra.dim, SL);
   if (rpt == 4) return launch_rec_scan_t<KIND, 4, CB, SL>(ra, grid, block, smem, st);
   if (rpt == 8) return launch_rec_scan_t<KIND, 8, CB, SL>(ra, grid, block, smem, st);
@@ -495,7 +547,7 @@ int launch_rec_scan(mtx_layered* e, RecScanArgs& ra, int n_runs, int rows, cudaS
   const bool wide = (long long)n_runs * ra.heads * ((ra.vdim + 15) / 16) >= 2LL * e->num_sms;
   static const int force_sl = env_int("MTX_REC_SLICES", 0);
   const bool fine = force_sl ? force_sl == 16 : (!wide && ra.dim >= 64 && columns * 8 < 512LL * e->num_sms);
-  ra.chunk = rec_chunk_tokens(ra.dim, wide ? 16 : 8, fine ? 16 : 8, rows == n_runs);
+  ra.chunk = rec_chunk_tokens(ra.dim, wide ? 16 : 8, fine ? 16 : 8, rows == n_runs, KIND == REC_DELTA ? 5 : 3);
   if (fine && ra.dim >= 16) return launch_rec_scan_cb<KIND, 8, 16>(ra, n_runs, st);
   return wide ? launch_rec_scan_cb<KIND, 16, 8>(ra, n_runs, st) : launch_rec_scan_cb<KIND, 8, 8>(ra, n_runs, st);
 }
@@ -610,6 +662,31 @@ int launch_softmax_mma_any(const SoftmaxAttnArgs<bf16>& sa, const SoftmaxMmaPlan
   return fail(MTX_ERR_UNSUPPORTED, "no tensor-core attention for dim %d", sa.dim);
 }
 
+// causal softmax attention of the step's rows over the paged cache: the tensor-core kernels for bf16 engines whose head sizes they
+// are built for (single-token steps: the transposed kernel), else the fp32 row kernel
+template <typename T>
+int run_softmax_attention(mtx_layered* e, SoftmaxAttnArgs<T>& sa, const mtx_ragged_batch& b, cudaStream_t st) {
+  bool done = false;
+  if constexpr (sizeof(T) == 2) {
+    const SoftmaxMmaPlan plan = softmax_mma_plan(sa.heads, sa.kv_heads, sa.dim, sa.vdim);
+    static const int decode_arm = env_int("MTX_SOFTMAX_DECODE", 1);
+    if (plan.ok && use_softmax_mma() && sa.ld_out % 2 == 0) {
+      if (b.n_tiles == sa.rows && sa.heads / sa.kv_heads <= 8 && decode_arm) MTX_TRY(launch_softmax_decode(e, sa, plan.d16, st));
+      else MTX_TRY(launch_softmax_mma(e, sa, plan, b.n_tiles, b.n_tiles == sa.rows, st));
+      done = true;
+    }
+  }
+  const size_t smem = softmax_attn_smem_bytes(sa.dim, sa.vdim);
+  static size_t attr_bytes[2] = {0, 0};  // per instantiation (bf16, float)
+  size_t& have = attr_bytes[sizeof(T) == 4 ? 1 : 0];
+  if (smem > 48 * 1024 && smem > have) {
+    MTX_CUDA(cudaFuncSetAttribute(softmax_attention_rows_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    have = smem;
+  }
+  if (!done) MTX_TRY(launch(softmax_attention_rows_kernel<T>, dim3(b.n_tiles, sa.heads), dim3(kSmaxThreads), smem, st, sa));
+  return MTX_OK;
+}
+
 // a MTX_MIXER_COMPOSITE layer with MTX_NORM_SANDWICH norms; xa holds wnorm(x, norm1) on entry
 template <typename T>
 int composite_layer(mtx_layered* e, int li, const mtx_ragged_batch& b, cudaStream_t st) {
@@ -670,24 +747,7 @@ int composite_layer(mtx_layered* e, int li, const mtx_ragged_batch& b, cudaStrea
     sa.out_scale = a.out_scale;
     sa.splits = 1;
     sa.rows = rows;
-    bool done = false;
-    if constexpr (sizeof(T) == 2) {
-      const SoftmaxMmaPlan plan = softmax_mma_plan(a.heads, a.kv_heads, a.dim, a.vdim);
-      static const int decode_arm = env_int("MTX_SOFTMAX_DECODE", 1);
-      if (plan.ok && use_softmax_mma() && cc.k_out % 2 == 0) {
-        if (b.n_tiles == rows && a.heads / a.kv_heads <= 8 && decode_arm) MTX_TRY(launch_softmax_decode(e, sa, plan.d16, st));
-        else MTX_TRY(launch_softmax_mma(e, sa, plan, b.n_tiles, b.n_tiles == rows, st));
-        done = true;
-      }
-    }
-    const size_t smem = softmax_attn_smem_bytes(a.dim, a.vdim);
-    static size_t attr_bytes[2] = {0, 0};  // per instantiation (bf16, float)
-    size_t& have = attr_bytes[sizeof(T) == 4 ? 1 : 0];
-    if (smem > 48 * 1024 && smem > have) {
-      MTX_CUDA(cudaFuncSetAttribute(softmax_attention_rows_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-      have = smem;
-    }
-    if (!done) MTX_TRY(launch(softmax_attention_rows_kernel<T>, dim3(b.n_tiles, a.heads), dim3(kSmaxThreads), smem, st, sa));
+    MTX_TRY(run_softmax_attention<T>(e, sa, b, st));
   }
   if (l.rec.kind != 0) {
     const mtx_recurrent_desc& r = l.rec;
@@ -786,6 +846,276 @@ int composite_layer(mtx_layered* e, int li, const mtx_ragged_batch& b, cudaStrea
   return sandwich_step<T>(e, e->y, nullptr, l.norm2b, nullptr, li + 1, rows, st);
 }
 
+// Column layout of a MTX_NORM_PARALLEL layer's input projection, and the columns its mixer fills of the activation that the
+// shared output projection reads (the feed-forward's hidden units follow them).
+struct ParallelCols {
+  int aq = 0, ak = 0, av = 0, ag = 0;         // softmax attention: q, k, v, head gates
+  int lq = 0, lkv = 0, lg = 0;                // latent attention: query latent, key / value latent + rotated part, head gates
+  int rq = 0, rk = 0, rv = 0, rg = 0, ra = 0, rx = 0;  // delta rule: q, k, v, output gate, removal, decay down-projection
+  int n = 0, k_mix = 0;
+};
+
+ParallelCols parallel_cols(const mtx_layer_desc& l) {
+  ParallelCols pc;
+  int at = 0;
+  const mtx_softmax_attn_desc& a = l.attn;
+  const mtx_latent_attn_desc& m = l.latent;
+  const mtx_recurrent_desc& r = l.rec;
+  if (a.heads > 0) {
+    pc.aq = at;
+    at += a.heads * a.dim;
+    if (!a.shared_kv) {
+      pc.ak = at;
+      at += a.kv_heads * a.dim;
+      pc.av = at;
+      at += a.kv_heads * a.vdim;
+    }
+    pc.ag = at;
+    if (a.head_gate) at += a.heads;
+    pc.k_mix = a.heads * a.vdim;
+  } else if (m.heads > 0) {
+    pc.lq = at;
+    at += m.q_rank;
+    pc.lkv = at;
+    at += m.kv_rank + m.rot_dim;
+    pc.lg = at;
+    at += m.heads;
+    pc.k_mix = m.heads * m.vdim;
+  } else if (r.kind != 0) {
+    pc.rq = at;
+    at += r.heads * r.dim;
+    pc.rk = at;
+    at += r.heads * r.dim;
+    pc.rv = at;
+    at += r.heads * r.vdim;
+    pc.rg = at;
+    at += r.heads * r.vdim;
+    pc.ra = at;
+    at += r.heads * r.dim;
+    pc.rx = at;
+    at += r.decay_rank;
+    pc.k_mix = r.heads * r.vdim;
+  }
+  pc.n = at;
+  return pc;
+}
+
+// x += mult * y (y null: no update), then h = gnorm(x) with the weight of layer `next` (none after the last layer)
+int group_norm_step(mtx_layered* e, const float* y, float mult, int next, int rows, cudaStream_t st) {
+  const float* w = next < e->cfg.num_layers ? e->layers[next].norm1 : nullptr;
+  if (!y && !w) return MTX_OK;
+  return launch(group_norm_step_kernel, dim3(rows), dim3(256), 0, st, y, mult, e->x, w, e->cfg.eps, e->h, e->cfg.width, e->cfg.norm_groups);
+}
+
+// a MTX_NORM_PARALLEL layer; h holds gnorm(x, norm1) on entry
+template <typename T>
+int parallel_layer(mtx_layered* e, int li, const mtx_ragged_batch& b, cudaStream_t st) {
+  const mtx_layered_config& c = e->cfg;
+  const mtx_layer_desc& l = e->layers[li];
+  const int rows = b.rows, E = c.width;
+  T* xa = static_cast<T*>(e->xa);  // the mixer's input
+  T* xb = static_cast<T*>(e->xb);  // the feed-forward's input
+  const ParallelCols pc = parallel_cols(l);
+  const int n_in = l.n_in, k_cat = pc.k_mix + l.ff;
+  T* cat = static_cast<T*>(e->attn);  // [rows, k_cat]: the mixer's heads, then the feed-forward's hidden units
+  InputConvArgs<T> ca;
+  memset(&ca, 0, sizeof(ca));
+  ca.h = e->h;
+  ca.w1 = l.conv1;
+  ca.w2 = l.ff > 0 ? l.conv2 : nullptr;
+  ca.state = l.conv_state;
+  ca.out1 = xa;
+  ca.out2 = xb;
+  ca.group = b.group;
+  ca.pos = b.pos;
+  ca.rows = rows;
+  ca.width = E;
+  ca.taps = l.conv_taps;
+  MTX_TRY(launch(input_conv_kernel<T>, dim3(rows), dim3(256), 0, st, ca));
+  if (l.conv_taps > 1)
+    MTX_TRY(launch(conv_state_update_kernel, dim3(b.n_runs, l.conv_taps - 1), dim3(256), 0, st, (const float*)e->h, l.conv_state, b.run_row0, b.group, b.pos, E,
+                   l.conv_taps));
+  MTX_TRY((linear<T, LIN_PLAIN>(e, xa, l.w_in, nullptr, e->qkv, nullptr, rows, n_in, E, st)));
+  SoftmaxAttnArgs<T> sa;
+  memset(&sa, 0, sizeof(sa));
+  sa.group = b.group;
+  sa.pos = b.pos;
+  sa.page_map = b.page_map;
+  sa.tile_row0 = b.tile_row0;
+  sa.num_pages = c.num_pages;
+  sa.tokens_per_page = c.tokens_per_page;
+  sa.max_pages = c.max_pages_per_group;
+  sa.out_scale = 1.0f;
+  sa.splits = 1;
+  sa.rows = rows;
+  sa.ld_gate = n_in;
+  if (l.attn.heads > 0) {
+    const mtx_softmax_attn_desc& a = l.attn;
+    QkPrepareArgs<T> qa;
+    memset(&qa, 0, sizeof(qa));
+    qa.proj = e->qkv;
+    qa.ld = n_in;
+    qa.q_col = pc.aq;
+    qa.k_col = pc.ak;
+    qa.v_col = pc.av;
+    qa.q_norm = a.q_norm;
+    qa.k_norm = a.k_norm;
+    qa.rot_freq = a.rot_freq;
+    qa.q_out = static_cast<T*>(e->q);
+    qa.k_pages = static_cast<T*>(a.k_pages);
+    qa.v_pages = static_cast<T*>(a.v_pages);
+    qa.group = b.group;
+    qa.pos = b.pos;
+    qa.page_map = b.page_map;
+    qa.heads = a.heads;
+    qa.kv_heads = a.kv_heads;
+    qa.dim = a.dim;
+    qa.vdim = a.vdim;
+    qa.rot_dims = a.rot_dims;
+    qa.rot_half = a.rot_half;
+    qa.shared_kv = a.shared_kv;
+    qa.num_pages = c.num_pages;
+    qa.tokens_per_page = c.tokens_per_page;
+    qa.max_pages = c.max_pages_per_group;
+    qa.eps = c.eps;
+    MTX_TRY(launch(qk_prepare_append_kernel<T>, dim3(rows), dim3(256), 0, st, qa));
+    sa.q = static_cast<const T*>(e->q);
+    sa.out = cat;
+    sa.ld_out = k_cat;
+    sa.k_pages = static_cast<const T*>(a.k_pages);
+    sa.v_pages = static_cast<const T*>(a.v_pages);
+    sa.heads = a.heads;
+    sa.kv_heads = a.kv_heads;
+    sa.dim = a.dim;
+    sa.vdim = a.vdim;
+    sa.window = a.window;
+    sa.scale = a.scale;
+    sa.slopes = a.slopes;
+    sa.sink = a.sink;
+    sa.gate = a.head_gate ? e->qkv + pc.ag : nullptr;
+    MTX_TRY(run_softmax_attention<T>(e, sa, b, st));
+  } else if (l.latent.heads > 0) {
+    const mtx_latent_attn_desc& m = l.latent;
+    const int H = m.heads, dl = m.kv_rank + m.rot_dim, dq = m.dim + m.rot_dim;
+    T* cq = static_cast<T*>(e->act);        // [rows, q_rank]
+    T* q_plain = static_cast<T*>(e->lat_o);  // [rows, H * dim], consumed before the attention writes its result to the same plane
+    T* q_full = static_cast<T*>(e->q);       // [rows, H * dl]
+    T* o_lat = static_cast<T*>(e->lat_o);    // [rows, H * dl]
+    LatentPrepareArgs<T> la;
+    memset(&la, 0, sizeof(la));
+    la.proj = e->qkv;
+    la.ld = n_in;
+    la.q_col = pc.lq;
+    la.kv_col = pc.lkv;
+    la.q_rank = m.q_rank;
+    la.kv_rank = m.kv_rank;
+    la.rot_dim = m.rot_dim;
+    la.rot_half = m.rot_half;
+    la.q_norm = m.q_norm;
+    la.kv_norm = m.kv_norm;
+    la.rot_freq = m.rot_freq;
+    la.cq_out = cq;
+    la.pages = static_cast<T*>(m.pages);
+    la.group = b.group;
+    la.pos = b.pos;
+    la.page_map = b.page_map;
+    la.tokens_per_page = c.tokens_per_page;
+    la.max_pages = c.max_pages_per_group;
+    la.eps = c.eps;
+    MTX_TRY(launch(latent_prepare_kernel<T>, dim3(rows), dim3(256), 0, st, la));
+    MTX_TRY((linear<T, LIN_PLAIN>(e, cq, m.w_uq, nullptr, e->lat_q, nullptr, rows, H * dq, m.q_rank, st)));
+    LatentQueryArgs<T> lq;
+    memset(&lq, 0, sizeof(lq));
+    lq.q = e->lat_q;
+    lq.q_plain = q_plain;
+    lq.q_full = q_full;
+    lq.rot_freq = m.rot_freq;
+    lq.pos = b.pos;
+    lq.heads = H;
+    lq.dim = m.dim;
+    lq.rot_dim = m.rot_dim;
+    lq.kv_rank = m.kv_rank;
+    lq.rot_half = m.rot_half;
+    MTX_TRY(launch(latent_query_kernel<T>, dim3(rows), dim3(256), 0, st, lq));
+    // the plain query parts into the latent space, head by head
+    MTX_TRY(linear_batched<T>(q_plain, (long long)H * m.dim, m.dim, m.w_uk_t, (long long)m.kv_rank * m.dim, q_full, (long long)H * dl, dl, rows, m.kv_rank,
+                              m.dim, H, st));
+    sa.q = q_full;
+    sa.out = o_lat;
+    sa.ld_out = (long long)H * dl;
+    sa.k_pages = static_cast<const T*>(m.pages);
+    sa.v_pages = static_cast<const T*>(m.pages);  // the values are the cached rows themselves
+    sa.heads = H;
+    sa.kv_heads = 1;
+    sa.dim = dl;
+    sa.vdim = dl;
+    sa.window = 0;
+    sa.scale = m.scale;
+    sa.sink = m.sink;
+    sa.gate = e->qkv + pc.lg;
+    MTX_TRY(run_softmax_attention<T>(e, sa, b, st));
+    // ... and the weighted latents out of it
+    MTX_TRY(linear_batched<T>(o_lat, (long long)H * dl, dl, m.w_uv, (long long)m.vdim * m.kv_rank, cat, k_cat, m.vdim, rows, m.vdim, m.kv_rank, H, st));
+  } else {
+    const mtx_recurrent_desc& r = l.rec;
+    DeltaPrepareArgs pa;
+    memset(&pa, 0, sizeof(pa));
+    pa.proj = e->qkv;
+    pa.ld = n_in;
+    pa.k_col = pc.rk;
+    pa.a_col = pc.ra;
+    pa.x_col = pc.rx;
+    pa.heads = r.heads;
+    pa.dim = r.dim;
+    pa.rank = r.decay_rank;
+    pa.rate = r.decay_rate;
+    pa.key_eps = r.key_eps;
+    pa.up_t = r.decay_up_t;
+    pa.w_bias = r.decay_bias;
+    pa.a_bias = r.gate_bias;
+    pa.out = e->rec_aux;
+    MTX_TRY(launch(delta_prepare_kernel, dim3(rows), dim3(256), sizeof(float) * r.decay_rank, st, pa));
+    RecScanArgs ra;
+    memset(&ra, 0, sizeof(ra));
+    ra.proj = e->qkv;
+    ra.ld = n_in;
+    ra.q_col = pc.rq;
+    ra.k_col = pc.rk;
+    ra.v_col = pc.rv;
+    ra.aux = e->rec_aux;
+    ra.o = e->rec_o;
+    ra.state_s = r.state_s;
+    ra.run_row0 = b.run_row0;
+    ra.group = b.group;
+    ra.pos = b.pos;
+    ra.heads = r.heads;
+    ra.dim = r.dim;
+    ra.vdim = r.vdim;
+    ra.q_scale = r.q_scale;
+    ra.vec4 = (n_in % 4 == 0 && pc.rq % 4 == 0 && pc.rk % 4 == 0 && pc.rv % 4 == 0 && r.dim % 4 == 0 && r.vdim % 4 == 0) ? 1 : 0;
+    MTX_TRY(launch_rec_scan<REC_DELTA>(e, ra, b.n_runs, rows, st));
+    RecOutArgs<T> oa;
+    memset(&oa, 0, sizeof(oa));
+    oa.o = e->rec_o;
+    oa.proj = e->qkv;
+    oa.ld = n_in;
+    oa.g_col = pc.rg;
+    oa.weight = r.out_norm;
+    oa.out = cat;
+    oa.ld_out = k_cat;
+    oa.out_col = 0;
+    oa.heads = r.heads;
+    oa.vdim = r.vdim;
+    oa.gate_silu = r.gate_silu;
+    oa.eps = c.eps;
+    oa.out_scale = r.out_scale;
+    MTX_TRY(launch(recurrent_out_kernel<T>, dim3(rows), dim3(256), 0, st, oa));
+  }
+  if (l.ff > 0) MTX_TRY((linear<T, LIN_RELU2>(e, xb, l.w_gate_up, nullptr, nullptr, cat + pc.k_mix, rows, l.ff, E, st, 0.0f, k_cat)));
+  MTX_TRY((linear<T, LIN_PLAIN>(e, cat, l.wo, nullptr, e->y, nullptr, rows, E, k_cat, st)));
+  return group_norm_step(e, e->y, l.residual_mult, li + 1, rows, st);
+}
+
 template <typename T>
 int step_typed(mtx_layered* e, const mtx_ragged_batch& b, cudaStream_t st) {
   const mtx_layered_config& c = e->cfg;
@@ -794,19 +1124,24 @@ int step_typed(mtx_layered* e, const mtx_ragged_batch& b, cudaStream_t st) {
   MTX_TRY(launch(embed_rows_kernel<T>, dim3(rows), dim3(128), 0, st, b.token, static_cast<const T*>(c.embedding), c.vocab, c.embed_scale, e->x, xa, E,
                  e->sandwich ? e->x0 : (float*)nullptr));
   if (e->sandwich) MTX_TRY(sandwich_step<T>(e, nullptr, nullptr, nullptr, nullptr, 0, rows, st));  // layer 0's pre-adds and pre-norm
+  if (e->parallel) MTX_TRY(group_norm_step(e, nullptr, 0.0f, 0, rows, st));                         // layer 0's norm
   for (int li = 0; li < c.num_layers; ++li) {
-    if (e->layers[li].mixer == MTX_MIXER_COMPOSITE) MTX_TRY(composite_layer<T>(e, li, b, st));
+    if (e->layers[li].norm_style == MTX_NORM_PARALLEL) MTX_TRY(parallel_layer<T>(e, li, b, st));
+    else if (e->layers[li].mixer == MTX_MIXER_COMPOSITE) MTX_TRY(composite_layer<T>(e, li, b, st));
     else MTX_TRY(window_layer<T>(e, li, b, st));
   }
   if (b.n_want > 0) {
     T* wn = static_cast<T*>(e->wanted);
-    if (c.final_norm) MTX_TRY(launch(weighted_norm_rows_kernel<T>, dim3(b.n_want), dim3(256), 0, st, (const float*)e->x, b.want_rows, c.final_norm, c.eps, wn, E));
+    if (e->parallel) MTX_TRY(launch(group_norm_rows_kernel<T>, dim3(b.n_want), dim3(256), 0, st, (const float*)e->x, b.want_rows, c.final_norm, c.eps, wn, E, c.norm_groups));
+    else if (c.final_norm) MTX_TRY(launch(weighted_norm_rows_kernel<T>, dim3(b.n_want), dim3(256), 0, st, (const float*)e->x, b.want_rows, c.final_norm, c.eps, wn, E));
     else MTX_TRY(launch(scalar_norm_rows_kernel<T>, dim3(b.n_want), dim3(256), 0, st, (const float*)e->x, b.want_rows, c.final_gain, c.eps, wn, E));
     MTX_TRY((linear<T, LIN_PLAIN>(e, wn, c.head, nullptr, b.logits, nullptr, b.n_want, c.vocab, E, st)));
-    if (c.logit_softcap > 0.0f) {
+    const float logit_scale = c.logit_scale != 0.0f ? c.logit_scale : 1.0f;
+    if (c.logit_softcap > 0.0f || logit_scale != 1.0f) {
       const long long total = (long long)b.n_want * c.vocab;
       const int blocks = int((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
-      MTX_TRY(launch(softcap_kernel, dim3(blocks), dim3(256), 0, st, b.logits, c.logit_softcap, total));
+      if (logit_scale != 1.0f) MTX_TRY(launch(logit_post_kernel, dim3(blocks), dim3(256), 0, st, b.logits, logit_scale, c.logit_softcap, total));
+      else MTX_TRY(launch(softcap_kernel, dim3(blocks), dim3(256), 0, st, b.logits, c.logit_softcap, total));
     }
   }
   return MTX_OK;
@@ -869,6 +1204,61 @@ int check_composite(mtx_layered* e, int i) {
   return MTX_OK;
 }
 
+// validation and workspace sizes of a MTX_NORM_PARALLEL layer
+int check_parallel(mtx_layered* e, int i) {
+  const mtx_layered_config& c = e->cfg;
+  const mtx_layer_desc& l = e->layers[i];
+  const mtx_softmax_attn_desc& a = l.attn;
+  const mtx_latent_attn_desc& m = l.latent;
+  const mtx_recurrent_desc& r = l.rec;
+  if (l.mixer != MTX_MIXER_COMPOSITE) return fail(MTX_ERR_UNSUPPORTED, "layer %d: a parallel layer has a composite mixer", i);
+  if (c.norm_groups < 1 || c.width % c.norm_groups != 0) return fail(MTX_ERR_ARG, "norm_groups = %d does not divide the width %d", c.norm_groups, c.width);
+  if (!l.norm1 || !l.w_in || !l.wo) return fail(MTX_ERR_ARG, "layer %d: the norm weight or a projection is missing", i);
+  if (l.conv_taps < 1 || !l.conv1 || (l.conv_taps > 1 && !l.conv_state)) return fail(MTX_ERR_ARG, "layer %d: the input convolution's taps / weights / state", i);
+  const int kinds = (a.heads > 0) + (m.heads > 0) + (r.kind != 0);
+  if (kinds != 1) return fail(MTX_ERR_ARG, "layer %d: a parallel layer has exactly one mixer", i);
+  if (a.heads > 0) {
+    if (a.kv_heads < 1 || a.heads % a.kv_heads != 0 || a.dim < 1 || a.vdim < 1 || a.window < 0) return fail(MTX_ERR_ARG, "layer %d: bad attention geometry", i);
+    if (a.rot_dims < 0 || a.rot_dims > a.dim || (a.rot_dims & 1) || (a.rot_dims > 0 && !a.rot_freq)) return fail(MTX_ERR_ARG, "layer %d: bad rot_dims / rot_freq", i);
+    if (a.values_are_keys) return fail(MTX_ERR_UNSUPPORTED, "layer %d: values_are_keys belongs to sandwich layers", i);
+    if (!a.k_pages || !a.v_pages) return fail(MTX_ERR_ARG, "layer %d: a page pool is missing", i);
+    if (kSmaxRows * a.vdim > kSmaxThreads * kSmaxMaxAcc) return fail(MTX_ERR_UNSUPPORTED, "layer %d: vdim %d exceeds %d", i, a.vdim, kSmaxThreads * kSmaxMaxAcc / kSmaxRows);
+    if (softmax_attn_smem_bytes(a.dim, a.vdim) > 200 * 1024) return fail(MTX_ERR_UNSUPPORTED, "layer %d: the attention's heads do not fit shared memory", i);
+    if (a.heads * a.dim > e->max_qdim) e->max_qdim = a.heads * a.dim;
+    if (a.heads > e->max_attn_heads) e->max_attn_heads = a.heads;
+  }
+  if (m.heads > 0) {
+    if (m.dim < 1 || m.rot_dim < 0 || m.vdim < 1 || m.q_rank < 1 || m.kv_rank < 1) return fail(MTX_ERR_ARG, "layer %d: bad latent attention geometry", i);
+    if (m.rot_dim > 0 && !m.rot_freq) return fail(MTX_ERR_ARG, "layer %d: rot_freq is missing", i);
+    if (!m.q_norm || !m.kv_norm || !m.w_uq || !m.w_uk_t || !m.w_uv || !m.pages) return fail(MTX_ERR_ARG, "layer %d: a latent attention weight or its pool is missing", i);
+    const int dl = m.kv_rank + m.rot_dim;
+    if (kSmaxRows * dl > kSmaxThreads * kSmaxMaxAcc) return fail(MTX_ERR_UNSUPPORTED, "layer %d: kv_rank + rot_dim = %d exceeds %d", i, dl, kSmaxThreads * kSmaxMaxAcc / kSmaxRows);
+    if (softmax_attn_smem_bytes(dl, dl) > 200 * 1024) return fail(MTX_ERR_UNSUPPORTED, "layer %d: the latent rows do not fit shared memory", i);
+    if (m.heads * dl > e->max_qdim) e->max_qdim = m.heads * dl;
+    if (m.heads * dl > e->max_lat_o) e->max_lat_o = m.heads * dl;
+    if (m.heads * m.dim > e->max_lat_o) e->max_lat_o = m.heads * m.dim;
+    if (m.heads * (m.dim + m.rot_dim) > e->max_lat_q) e->max_lat_q = m.heads * (m.dim + m.rot_dim);
+    if (m.q_rank > e->max_ff) e->max_ff = m.q_rank;  // (the query latent waits in the plane of the feed-forward's activation)
+    if (m.heads > e->max_attn_heads) e->max_attn_heads = m.heads;
+  }
+  if (r.kind != 0) {
+    if (r.kind != MTX_REC_DELTA) return fail(MTX_ERR_UNSUPPORTED, "layer %d: a parallel layer's recurrence is the delta rule", i);
+    if (r.heads < 1 || r.dim < 1 || r.vdim < 1 || r.dim > kRecSlices * 32) return fail(MTX_ERR_UNSUPPORTED, "layer %d: recurrence heads / dim (<= %d) / vdim", i, kRecSlices * 32);
+    if (!r.state_s || !r.out_norm || r.decay_rank < 1 || !r.decay_up_t) return fail(MTX_ERR_ARG, "layer %d: the recurrence's state, output norm or decay projection is missing", i);
+    if (r.heads * r.vdim > e->max_rec_o) e->max_rec_o = r.heads * r.vdim;
+    if (3 * r.heads * r.dim > e->max_rec_aux) e->max_rec_aux = 3 * r.heads * r.dim;
+  }
+  const ParallelCols pc = parallel_cols(l);
+  if (l.n_in < pc.n) return fail(MTX_ERR_ARG, "layer %d: n_in = %d, the mixer needs %d projection rows", i, l.n_in, pc.n);
+  if (l.n_in > e->max_nqkv) e->max_nqkv = l.n_in;
+  if (l.ff < 0 || (l.ff > 0 && (l.ff_kind != MTX_FF_RELU2 || !l.w_gate_up))) return fail(MTX_ERR_ARG, "layer %d: a parallel layer's feed-forward is down(relu(up x)^2)", i);
+  if (pc.k_mix + l.ff > e->max_odim) e->max_odim = pc.k_mix + l.ff;
+  if (l.ff > e->max_nqkv) e->max_nqkv = l.ff;  // (a tcgen05 projection parks its bf16 result in a plane of max_nqkv columns)
+  if (m.heads > 0 && m.heads * (m.dim + m.rot_dim) > e->max_nqkv) e->max_nqkv = m.heads * (m.dim + m.rot_dim);
+  e->parallel = true;
+  return MTX_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -886,8 +1276,8 @@ int mtx_layered_create(const mtx_layered_config* cfg, const mtx_layer_desc* laye
   for (int i = 0; i < c.num_layers; ++i) {
     const mtx_layer_desc& l = e->layers[i];
     int rc = MTX_OK;
-    if (l.mixer == MTX_MIXER_COMPOSITE) {
-      rc = check_composite(e, i);
+    if (l.norm_style == MTX_NORM_PARALLEL || l.mixer == MTX_MIXER_COMPOSITE) {
+      rc = l.norm_style == MTX_NORM_PARALLEL ? check_parallel(e, i) : check_composite(e, i);
       if (rc != MTX_OK) {
         delete e;
         return rc;
@@ -929,6 +1319,15 @@ int mtx_layered_create(const mtx_layered_config* cfg, const mtx_layer_desc* laye
       delete e;
       return fail(MTX_ERR_UNSUPPORTED, "layer %d: all layers of a model share one norm style", i);
     }
+  for (int i = 0; i < c.num_layers; ++i)
+    if ((e->layers[i].norm_style == MTX_NORM_PARALLEL) != e->parallel) {
+      delete e;
+      return fail(MTX_ERR_UNSUPPORTED, "layer %d: all layers of a model share one norm style", i);
+    }
+  if (e->parallel && !c.final_norm) {
+    delete e;
+    return fail(MTX_ERR_ARG, "a model of parallel layers has a final norm weight");
+  }
   if (e->sandwich && c.width > 256 * kSandwichMax) {
     delete e;
     return fail(MTX_ERR_UNSUPPORTED, "width %d exceeds %d", c.width, 256 * kSandwichMax);
@@ -982,6 +1381,10 @@ int mtx_layered_bind(mtx_layered* e, void* workspace, size_t workspace_bytes) {
   e->moe_row = reinterpret_cast<int*>(base + L.moe_row);
   e->moe_off = reinterpret_cast<int*>(base + L.moe_off);
   e->moe_act = base + L.moe_act;
+  e->h = reinterpret_cast<float*>(base + L.h);
+  e->xb = base + L.xb;
+  e->lat_q = reinterpret_cast<float*>(base + L.lat_q);
+  e->lat_o = base + L.lat_o;
   e->bound = true;
   return MTX_OK;
 }
@@ -992,7 +1395,7 @@ int mtx_layered_step(mtx_layered* e, const mtx_ragged_batch* b, mtx_stream strea
   if (b->n_want < 0 || b->n_want > e->cfg.max_want) return fail(MTX_ERR_ARG, "n_want = %d outside [0, %d]", b->n_want, e->cfg.max_want);
   if (!b->token || !b->group || !b->pos || !b->page_map || (b->n_want > 0 && (!b->want_rows || !b->logits))) return fail(MTX_ERR_ARG, "null batch array");
   if (b->n_tiles < 0 || b->n_tiles > b->rows) return fail(MTX_ERR_ARG, "n_tiles = %d for %d rows", b->n_tiles, b->rows);
-  if (e->sandwich && (b->n_tiles < 1 || !b->tile_row0 || b->n_runs < 1 || b->n_runs > b->rows || !b->run_row0))
+  if ((e->sandwich || e->parallel) && (b->n_tiles < 1 || !b->tile_row0 || b->n_runs < 1 || b->n_runs > b->rows || !b->run_row0))
     return fail(MTX_ERR_ARG, "this model needs the batch's query tiles and runs");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   return e->cfg.float32 ? step_typed<float>(e, *b, st) : step_typed<bf16>(e, *b, st);

@@ -11,6 +11,12 @@
 //            LIN_BIAS   out = acc + bias[col]          (fp32)
 //            LIN_GATED  act[r, f] = gelu_tanh(acc[r, 2f]) * acc[r, 2f + 1]   (the weight rows are interleaved gate / up)
 //            LIN_GATED_CLAMP  act[r, f] = g sigmoid(1.702 g) (u + 1), g = min(acc[r, 2f], limit), u = clamp(acc[r, 2f + 1], -limit, limit)
+//            LIN_ACT    act[r, c] = acc                  (in the matmul dtype, row pitch ldo: the input of another product)
+//            LIN_RELU2  act[r, c] = max(acc, 0)^2
+//
+// Batched mode (batch_a != 0 or batch_o != 0; group_off null): blockIdx.z names one of several products over the same rows whose
+// operands lie side by side: `a` moves by batch_a columns, the weight by w_group_stride elements and the output by batch_o columns
+// per batch (the per-head products of an attention that works in a latent space).
 //
 // Grouped mode (group_off != null; a mixture of experts): blockIdx.z names a group with its own weight matrix; the group's rows are
 // the slots [group_off[g], group_off[g + 1]); slot s reads row a_row[s] of `a` (or row s when a_row is null) and writes row s of the
@@ -21,7 +27,7 @@
 
 namespace mtx {
 
-enum { LIN_PLAIN = 0, LIN_BIAS = 1, LIN_GATED = 2, LIN_GATED_CLAMP = 3 };
+enum { LIN_PLAIN = 0, LIN_BIAS = 1, LIN_GATED = 2, LIN_GATED_CLAMP = 3, LIN_ACT = 4, LIN_RELU2 = 5 };
 
 template <typename T>
 struct LinArgs {
@@ -35,13 +41,23 @@ struct LinArgs {
   float limit;             // LIN_GATED_CLAMP
   const int* group_off;    // grouped mode: [groups + 1] slot ranges
   const int* a_row;        // grouped mode: [slots] row of `a` per slot, or null
-  long long w_group_stride;  // grouped mode: elements between two groups' weights
+  long long w_group_stride;  // grouped / batched mode: elements between two groups' weights
+  long long batch_a, batch_o;  // batched mode: columns between two batches' inputs / outputs
 };
 
 // grouped mode: the argument block of this CTA's group (false: the CTA has no rows)
 template <typename T>
 __device__ __forceinline__ bool lin_enter_group(LinArgs<T>& p, int tile_rows) {
-  if (p.group_off == nullptr) return true;
+  if (p.group_off == nullptr) {
+    if (p.batch_a != 0 || p.batch_o != 0) {
+      const size_t b = blockIdx.z;
+      p.a += b * p.batch_a;
+      p.w += b * p.w_group_stride;
+      if (p.out) p.out += b * p.batch_o;
+      if (p.act) p.act += b * p.batch_o;
+    }
+    return true;
+  }
   const int g = blockIdx.z, s0 = p.group_off[g], cnt = p.group_off[g + 1] - s0;
   if (int(blockIdx.y) * tile_rows >= cnt) return false;
   p.rows = cnt;
@@ -84,6 +100,18 @@ __device__ __forceinline__ void lin_store_pair(const LinArgs<T>& p, int r, int c
   }
   if (EPI == LIN_GATED_CLAMP) {
     p.act[size_t(r) * p.ldo + (c >> 1)] = to_act<T>(clamped_gate_f(v0, v1, p.limit));
+    return;
+  }
+  if (EPI == LIN_ACT || EPI == LIN_RELU2) {
+    if (EPI == LIN_RELU2) {
+      v0 = fmaxf(v0, 0.0f);
+      v1 = fmaxf(v1, 0.0f);
+      v0 *= v0;
+      v1 *= v1;
+    }
+    T* o = p.act + size_t(r) * p.ldo + c;
+    o[0] = to_act<T>(v0);
+    if (c + 1 < p.n) o[1] = to_act<T>(v1);
     return;
   }
   float* o = p.out + size_t(r) * p.ldo + c;

@@ -5,6 +5,8 @@
 //   GLA    S <- diag(a) S + k v^T,  o = S^T q                      a = sigmoid(z)^(1 / tau) per key channel
 //   mLSTM  m' = max(f + m, i);  S <- e^(f + m - m') S + e^(i - m') k v^T;  n likewise with k alone;
 //          o = S^T q / (max(|n . q|, e^(-m')) + denom_eps)          (m starts at 0; i, f are log gates)
+//   delta  S <- diag(w) S' - (a u)(u^T S') + k v^T,  o = S^T q    (S' the old state in both first terms)
+//          u = k / sqrt(|k|^2 + key_eps); w = exp(-rate sigmoid(z)), z = up tanh(down x) + bias; a = sigmoid(. + bias), per key channel
 //
 // A run (consecutive rows of one sequence) is walked in order from the group's state; a run that starts at position 0 starts
 // from zero instead, so a slot that is handed to another sequence needs no clearing.  Every value column of S is independent of
@@ -13,6 +15,7 @@
 // tokens in order.  The result of a token is the same bits however the sequence is cut into steps.
 //
 //   recurrent_prepare_kernel   per row: the GLA's decays (low-rank up-projection, bias, sigmoid^(1/tau)) or the mLSTM's two log gates
+//   delta_prepare_kernel       per row: the delta rule's decays, unit keys and removal vectors a u
 //   recurrent_scan_kernel      the walk
 //   recurrent_out_kernel<T>    per row and head: o / rms(o) * weight * gate(g) * out_scale -> the activation of the output projection
 #pragma once
@@ -23,7 +26,7 @@
 
 namespace mtx {
 
-enum { REC_GLA = 1, REC_MLSTM = 2 };
+enum { REC_GLA = 1, REC_MLSTM = 2, REC_DELTA = 3 };
 
 __device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.0f) - log1pf(expf(-fabsf(z))); }
 
@@ -63,6 +66,46 @@ __global__ void __launch_bounds__(256) recurrent_prepare_kernel(const RecPrepare
   }
 }
 
+struct DeltaPrepareArgs {
+  const float* proj;   // [rows, ld]: keys at k_col, removal pre-activations at a_col (heads * dim each), the decay's down-projection at x_col (rank)
+  long long ld;
+  int k_col, a_col, x_col;
+  int heads, dim, rank;
+  float rate, key_eps;
+  const float* up_t;   // [rank, heads * dim]
+  const float* w_bias; // [heads * dim]
+  const float* a_bias; // [heads * dim]
+  float* out;          // [rows, 3, heads * dim]: decays w, unit keys u, removal vectors a * u
+};
+
+// one CTA per row, a warp per head
+__global__ void __launch_bounds__(256) delta_prepare_kernel(const DeltaPrepareArgs a) {
+  extern __shared__ float s_low[];
+  griddep_wait();
+  const int r = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, d = a.dim, n = a.heads * d;
+  const float* row = a.proj + size_t(r) * a.ld;
+  for (int e = threadIdx.x; e < a.rank; e += blockDim.x) s_low[e] = tanhf(row[a.x_col + e]);
+  __syncthreads();
+  float* out = a.out + size_t(r) * 3 * n;
+  for (int h = warp; h < a.heads; h += 8) {
+    const float* k = row + a.k_col + h * d;
+    float ss = 0.0f;
+    for (int c = lane; c < d; c += 32) ss = fmaf(k[c], k[c], ss);
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss + a.key_eps);
+    for (int c = lane; c < d; c += 32) {
+      const int col = h * d + c;
+      float z = a.w_bias ? a.w_bias[col] : 0.0f;
+      for (int e = 0; e < a.rank; ++e) z = fmaf(a.up_t[size_t(e) * n + col], s_low[e], z);
+      const float u = k[c] * inv;
+      const float rem = 1.0f / (1.0f + expf(-(row[a.a_col + col] + (a.a_bias ? a.a_bias[col] : 0.0f))));
+      out[col] = expf(-a.rate / (1.0f + expf(-z)));
+      out[n + col] = u;
+      out[2 * n + col] = rem * u;
+    }
+  }
+}
+
 struct RecScanArgs {
   const float* proj;   // [rows, ld]: q at q_col, k at k_col, v at v_col (heads x dim, heads x dim, heads x vdim)
   long long ld;
@@ -89,21 +132,22 @@ constexpr int kRecSlices = 8, kRecUnroll = 4;  // (kRecSlices: the default; shor
 
 // floats of one token in a stage: q, k, decays (8 * RPT channels each), then CB values, then 4 scalars (mLSTM: log input gate,
 // log forget gate; later keep, put, floor)
-__host__ __device__ inline int rec_token_floats(int rpt, int cb, int sl) { return 3 * sl * rpt + cb + 4; }
+// (nvec per-channel vectors: q, k, decays; the delta rule also stages u and a u)
+__host__ __device__ inline int rec_token_floats(int rpt, int cb, int sl, int nvec = 3) { return nvec * sl * rpt + cb + 4; }
 inline int rec_rpt(int dim, int sl) {
   const int r = (dim + sl - 1) / sl;
   return r <= 4 ? 4 : (r <= 8 ? 8 : (r <= 16 ? 16 : 32));
 }
 constexpr int kRecStages = 4;  // chunks in the cp.async ring: three are in flight while one is walked
 // tokens per chunk: 16 for prompt portions (as many as 96 KB of ring hold, at least 4), 4 when every run is a single token
-inline int rec_chunk_tokens(int dim, int cb, int sl, bool single_tokens) {
+inline int rec_chunk_tokens(int dim, int cb, int sl, bool single_tokens, int nvec = 3) {
   if (single_tokens) return kRecUnroll;
-  int t = (96 * 1024) / int(sizeof(float) * kRecStages * rec_token_floats(rec_rpt(dim, sl), cb, sl));
+  int t = (96 * 1024) / int(sizeof(float) * kRecStages * rec_token_floats(rec_rpt(dim, sl), cb, sl, nvec));
   t = t / kRecUnroll * kRecUnroll;
   return t > 16 ? 16 : (t < kRecUnroll ? kRecUnroll : t);
 }
-inline size_t rec_scan_smem_bytes(int dim, int cb, int sl, int chunk) {
-  return sizeof(float) * kRecStages * size_t(chunk) * rec_token_floats(rec_rpt(dim, sl), cb, sl);
+inline size_t rec_scan_smem_bytes(int dim, int cb, int sl, int chunk, int nvec = 3) {
+  return sizeof(float) * kRecStages * size_t(chunk) * rec_token_floats(rec_rpt(dim, sl), cb, sl, nvec);
 }
 
 __device__ __forceinline__ void rec_cp_async_16(float* dst, const float* src) {
@@ -119,7 +163,8 @@ __device__ __forceinline__ void rec_cp_async_4(float* dst, const float* src) {
 template <int KIND, int RPT, int CB, int SL>
 __global__ void __launch_bounds__(CB * SL) recurrent_scan_kernel(const RecScanArgs a) {
   extern __shared__ __align__(16) float rec_smem[];
-  constexpr int NT = CB * SL, QP = SL * RPT, TF = 3 * QP + CB + 4, GS = 4 * SL;  // GS: channels per group of float4s
+  constexpr int NV = KIND == REC_DELTA ? 5 : 3;                                   // per-channel vectors of a staged token
+  constexpr int NT = CB * SL, QP = SL * RPT, TF = NV * QP + CB + 4, GS = 4 * SL;  // GS: channels per group of float4s
   const int d = a.dim, dv = a.vdim, H = a.heads, TC = a.chunk;
   const int tid = threadIdx.x, jl = tid / SL, sl = tid % SL;
   griddep_wait();
@@ -183,15 +228,25 @@ __global__ void __launch_bounds__(CB * SL) recurrent_scan_kernel(const RecScanAr
           rec_cp_async_16(dst, row + a.q_col + h * d + r);
           rec_cp_async_16(dst + QP, row + a.k_col + h * d + r);
           if (KIND == REC_GLA) rec_cp_async_16(dst + 2 * QP, a.aux + size_t(r0 + t0 + t) * H * d + h * d + r);
+          if (KIND == REC_DELTA) {
+            const float* ax = a.aux + size_t(r0 + t0 + t) * 3 * H * d + h * d + r;
+            rec_cp_async_16(dst + 2 * QP, ax);
+            rec_cp_async_16(dst + 3 * QP, ax + H * d);
+            rec_cp_async_16(dst + 4 * QP, ax + 2 * H * d);
+          }
         } else {
           *reinterpret_cast<float4*>(dst) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
           *reinterpret_cast<float4*>(dst + QP) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-          if (KIND == REC_GLA) *reinterpret_cast<float4*>(dst + 2 * QP) = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+          if (KIND == REC_GLA || KIND == REC_DELTA) *reinterpret_cast<float4*>(dst + 2 * QP) = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+          if (KIND == REC_DELTA) {
+            *reinterpret_cast<float4*>(dst + 3 * QP) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            *reinterpret_cast<float4*>(dst + 4 * QP) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          }
         }
       }
       for (int e = tid; e < TL * C4; e += NT) {
         const int t = e / C4, c2 = (e % C4) * 4;
-        float* dst = base + t * TF + 3 * QP + c2;
+        float* dst = base + t * TF + NV * QP + c2;
         if (t0 + t < nr && col0 + c2 < dv) rec_cp_async_16(dst, a.proj + size_t(r0 + t0 + t) * a.ld + a.v_col + h * dv + col0 + c2);
         else *reinterpret_cast<float4*>(dst) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
       }
@@ -205,15 +260,22 @@ __global__ void __launch_bounds__(CB * SL) recurrent_scan_kernel(const RecScanAr
         rec_cp_async_4(dst, row + a.q_col + h * d + r);
         rec_cp_async_4(dst + QP, row + a.k_col + h * d + r);
         if (KIND == REC_GLA) rec_cp_async_4(dst + 2 * QP, a.aux + size_t(r0 + t0 + t) * H * d + h * d + r);
+        if (KIND == REC_DELTA) {
+          const float* ax = a.aux + size_t(r0 + t0 + t) * 3 * H * d + h * d + r;
+          rec_cp_async_4(dst + 2 * QP, ax);
+          rec_cp_async_4(dst + 3 * QP, ax + H * d);
+          rec_cp_async_4(dst + 4 * QP, ax + 2 * H * d);
+        }
       } else {
         dst[0] = 0.0f;
         dst[QP] = 0.0f;
-        if (KIND == REC_GLA) dst[2 * QP] = 1.0f;
+        if (KIND == REC_GLA || KIND == REC_DELTA) dst[2 * QP] = 1.0f;
+        if (KIND == REC_DELTA) dst[3 * QP] = dst[4 * QP] = 0.0f;
       }
     }
     for (int e = tid; e < TL * CB; e += NT) {
       const int t = e / CB, c2 = e % CB;
-      float* dst = base + t * TF + 3 * QP + c2;
+      float* dst = base + t * TF + NV * QP + c2;
       if (t0 + t < nr && col0 + c2 < dv) rec_cp_async_4(dst, a.proj + size_t(r0 + t0 + t) * a.ld + a.v_col + h * dv + col0 + c2);
       else dst[0] = 0.0f;
     }
@@ -264,7 +326,7 @@ __global__ void __launch_bounds__(CB * SL) recurrent_scan_kernel(const RecScanAr
         const float* tok = base + (t + u) * TF;
         const float* q = tok + sl * 4;
         const float* k = q + QP;
-        const float v = tok[3 * QP + jl];
+        const float v = tok[NV * QP + jl];
         part[u] = 0.0f;
         npart[u] = 0.0f;
         floor_m[u] = 0.0f;
@@ -278,6 +340,35 @@ __global__ void __launch_bounds__(CB * SL) recurrent_scan_kernel(const RecScanAr
             S[i4 + 1] = fmaf(a4.y, S[i4 + 1], k4.y * v);
             S[i4 + 2] = fmaf(a4.z, S[i4 + 2], k4.z * v);
             S[i4 + 3] = fmaf(a4.w, S[i4 + 3], k4.w * v);
+            part[u] = fmaf(S[i4], q4.x, part[u]);
+            part[u] = fmaf(S[i4 + 1], q4.y, part[u]);
+            part[u] = fmaf(S[i4 + 2], q4.z, part[u]);
+            part[u] = fmaf(S[i4 + 3], q4.w, part[u]);
+          }
+        } else if (KIND == REC_DELTA) {
+          // what the old column holds along u, added over the column's slices, comes off along a u
+          const float* al = k + QP;
+          const float* un = k + 2 * QP;
+          const float* rm = k + 3 * QP;
+          float along = 0.0f;
+#pragma unroll
+          for (int i4 = 0; i4 < RPT; i4 += 4) {
+            const float4 u4 = *reinterpret_cast<const float4*>(un + i4 * SL);
+            along = fmaf(S[i4], u4.x, along);
+            along = fmaf(S[i4 + 1], u4.y, along);
+            along = fmaf(S[i4 + 2], u4.z, along);
+            along = fmaf(S[i4 + 3], u4.w, along);
+          }
+#pragma unroll
+          for (int o = 1; o < SL; o <<= 1) along += __shfl_xor_sync(0xffffffffu, along, o);
+#pragma unroll
+          for (int i4 = 0; i4 < RPT; i4 += 4) {
+            const float4 k4 = *reinterpret_cast<const float4*>(k + i4 * SL), q4 = *reinterpret_cast<const float4*>(q + i4 * SL),
+                         a4 = *reinterpret_cast<const float4*>(al + i4 * SL), r4 = *reinterpret_cast<const float4*>(rm + i4 * SL);
+            S[i4] = fmaf(a4.x, S[i4], fmaf(-r4.x, along, k4.x * v));
+            S[i4 + 1] = fmaf(a4.y, S[i4 + 1], fmaf(-r4.y, along, k4.y * v));
+            S[i4 + 2] = fmaf(a4.z, S[i4 + 2], fmaf(-r4.z, along, k4.z * v));
+            S[i4 + 3] = fmaf(a4.w, S[i4 + 3], fmaf(-r4.w, along, k4.w * v));
             part[u] = fmaf(S[i4], q4.x, part[u]);
             part[u] = fmaf(S[i4 + 1], q4.y, part[u]);
             part[u] = fmaf(S[i4 + 2], q4.z, part[u]);

@@ -11,7 +11,13 @@
 // sine and cosine in fp32; the remaining channels pass.  A design whose values are the un-rotated keys (values_are_keys) gets the key
 // projection written twice: rotated into the key pool, as projected into the value pool.
 //
+// Optional parts, each off when its pointer is null: a distance penalty slopes[h] * (i - j) taken off the scaled score; a sink
+// (exp(sink[h]) in the denominator, with no key and no value); a gate sigmoid(gate[row, h]) on head h's output; RMS norms of the
+// query and key heads before the rotation; the rotation's other pairing (i, i + rot_dims / 2); keys and values taken from the
+// pools of an earlier layer (the layer then appends nothing).
+//
 //   rope_append_kernel         per row: bias already in the projection; rotates q and k, writes q, appends k and v to the pages
+//   qk_prepare_append_kernel   the same with the optional head norms, either pairing, and layers that append nothing
 //   softmax_attention_rows_kernel<T>   one CTA per (query tile of <= 16 rows of one sequence, query head); keys walked in tiles
 //                              staged as fp32 in shared memory; running maximum and sum per row; everything fp32 (T is only the
 //                              dtype of q, the pools and the output).  Serves float32 engines, every geometry, and decode rows.
@@ -97,6 +103,71 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeAppendArgs<T
 }
 
 template <typename T>
+struct QkPrepareArgs {
+  const float* proj;     // [rows, ld]: q at column q_col, k at k_col, v at v_col
+  long long ld;
+  int q_col, k_col, v_col;
+  const float* q_norm;   // [d] or null
+  const float* k_norm;   // [d] or null
+  const double* rot_freq;  // [rot_dims / 2] (rot_dims == 0: null)
+  T* q_out;              // [rows, H * d]
+  T* k_pages;
+  T* v_pages;
+  const int* group;
+  const int* pos;
+  const int* page_map;
+  int heads, kv_heads, dim, vdim, rot_dims, rot_half, shared_kv;
+  int num_pages, tokens_per_page, max_pages;
+  float eps;
+};
+
+// angle of channel pair c at position p, reduced to [-pi, pi] in double before the fp32 sine and cosine
+__device__ __forceinline__ void rot_sincos(double p, double freq, float* sn, float* cs) {
+  const double ang = p * freq;
+  sincosf(float(ang - 6.283185307179586 * rint(ang * 0.15915494309189535)), sn, cs);
+}
+
+// one CTA per row, a warp per head (query heads, then key heads): norm, rotation, write; then the values
+template <typename T>
+__global__ void __launch_bounds__(256) qk_prepare_append_kernel(const QkPrepareArgs<T> a) {
+  griddep_wait();
+  const int r = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
+  const int H = a.heads, G = a.shared_kv ? 0 : a.kv_heads, d = a.dim, dv = a.vdim, rh = a.rot_dims / 2;
+  const float* row = a.proj + size_t(r) * a.ld;
+  const int p = a.pos[r], grp = a.group[r];
+  const size_t slot = size_t(a.page_map[size_t(grp) * a.max_pages + p / a.tokens_per_page]) * a.tokens_per_page + p % a.tokens_per_page;
+  const double dp = double(p);
+  for (int u = warp; u < H + G; u += nw) {
+    const bool is_q = u < H;
+    const float* src = row + (is_q ? a.q_col + u * d : a.k_col + (u - H) * d);
+    const float* w = is_q ? a.q_norm : a.k_norm;
+    float inv = 1.0f;
+    if (w) {
+      float ss = 0.0f;
+      for (int c = lane; c < d; c += 32) ss = fmaf(src[c], src[c], ss);
+      ss = warp_sum(ss);
+      inv = 1.0f / sqrtf(ss / float(d) + a.eps);
+    }
+    T* dst = is_q ? a.q_out + size_t(r) * H * d + u * d : a.k_pages + (size_t(u - H) * a.num_pages * a.tokens_per_page + slot) * d;
+    auto val = [&](int c) { return w ? src[c] * inv * w[c] : src[c]; };
+    for (int i = lane; i < rh; i += 32) {  // the pairs that turn
+      const int c0 = a.rot_half ? i : 2 * i, c1 = a.rot_half ? i + rh : 2 * i + 1;
+      float sn, cs;
+      rot_sincos(dp, a.rot_freq[i], &sn, &cs);
+      const float x0 = val(c0), x1 = val(c1);
+      dst[c0] = to_act<T>(x0 * cs - x1 * sn);
+      dst[c1] = to_act<T>(x1 * cs + x0 * sn);
+    }
+    for (int c = 2 * rh + lane; c < d; c += 32) dst[c] = to_act<T>(val(c));
+  }
+  if (a.shared_kv) return;
+  for (int e = tid; e < G * dv; e += blockDim.x) {
+    const int kv = e / dv, c = e % dv;
+    a.v_pages[(size_t(kv) * a.num_pages * a.tokens_per_page + slot) * dv + c] = to_act<T>(row[a.v_col + e]);
+  }
+}
+
+template <typename T>
 struct SoftmaxAttnArgs {
   const T* q;            // [rows, H * d]
   T* out;                // [rows, ld_out]; head h writes columns [h * dv, (h + 1) * dv)
@@ -115,7 +186,16 @@ struct SoftmaxAttnArgs {
   int splits, rows;
   float* part_o;   // [splits, rows, H, dv]
   float* part_ml;  // [splits, rows, H, 2]: running maximum, sum
+  // optional parts (null: none)
+  const float* slopes;  // [H]: slopes[h] * (i - j) is taken off the scaled score
+  const float* sink;    // [H]: exp(sink[h]) joins the denominator (it enters the first key split's running maximum and sum)
+  const float* gate;    // [rows, ld_gate]: head h's output is multiplied by sigmoid(gate[row, h])
+  long long ld_gate;
 };
+
+__device__ __forceinline__ float smax_gate(const float* gate, long long ld, int row, int h) {
+  return gate ? 1.0f / (1.0f + expf(-gate[size_t(row) * ld + h])) : 1.0f;
+}
 
 constexpr int kSmaxThreads = 256, kSmaxRows = 16, kSmaxKeys = 32;
 constexpr int kSmaxMaxAcc = 32;  // kSmaxRows * vdim <= kSmaxThreads * kSmaxMaxAcc: vdim <= 512
@@ -145,9 +225,10 @@ __global__ void __launch_bounds__(kSmaxThreads) softmax_attention_rows_kernel(co
   if (a.window > 0 && p0 - a.window + 1 > 0) lo = p0 - a.window + 1;
   for (int e = tid; e < nr * d; e += kSmaxThreads) sq[e] = act_f32(a.q[size_t(r0 + e / d) * a.heads * d + h * d + e % d]) * a.scale;
   if (tid < kSmaxRows) {
-    s_max[tid] = -INFINITY;
-    s_sum[tid] = 0.0f;
+    s_max[tid] = a.sink ? a.sink[h] : -INFINITY;
+    s_sum[tid] = a.sink ? 1.0f : 0.0f;
   }
+  const float slope = a.slopes ? a.slopes[h] : 0.0f;
   float acc[kSmaxMaxAcc];
 #pragma unroll
   for (int u = 0; u < kSmaxMaxAcc; ++u) acc[u] = 0.0f;
@@ -175,6 +256,7 @@ __global__ void __launch_bounds__(kSmaxThreads) softmax_attention_rows_kernel(co
         const float* kv = sk + jj * (d + 1);
         s = 0.0f;
         for (int c = 0; c < d; ++c) s = fmaf(qv[c], kv[c], s);
+        s -= slope * float(pi - j);
       }
       sp[e] = s;
     }
@@ -214,7 +296,7 @@ __global__ void __launch_bounds__(kSmaxThreads) softmax_attention_rows_kernel(co
     const int o = tid + u * kSmaxThreads;
     if (o < nr * dv) {
       const int i = o / dv, c = o % dv;
-      a.out[size_t(r0 + i) * a.ld_out + h * dv + c] = to_act<T>(acc[u] * a.out_scale / s_sum[i]);
+      a.out[size_t(r0 + i) * a.ld_out + h * dv + c] = to_act<T>(acc[u] * a.out_scale / s_sum[i] * smax_gate(a.gate, a.ld_gate, r0 + i, h));
     }
   }
 }
@@ -311,6 +393,11 @@ __global__ void __launch_bounds__(128) softmax_attention_mma_kernel(const Softma
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[nb][e] = 0.0f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+  if (a.sink && blockIdx.z == 0) {  // (the four lanes of a row are added at the end: lane t == 0 carries the sink's 1)
+    m_run[0] = m_run[1] = a.sink[h];
+    l_run[0] = l_run[1] = t == 0 ? 1.0f : 0.0f;
+  }
+  const float slope = a.slopes ? a.slopes[h] : 0.0f;
   const int pi0 = p0 + g, pi1 = p0 + g + 8;
 
   if (n_key_tiles > 0) load_tile(0, 0);
@@ -343,7 +430,7 @@ __global__ void __launch_bounds__(128) softmax_attention_mma_kernel(const Softma
         for (int e = 0; e < 4; ++e) {
           const int j = j0 + nb * 8 + 2 * t + (e & 1), pi = (e & 2) ? pi1 : pi0;
           const bool seen = j <= pi && (a.window <= 0 || pi - j < a.window);
-          s[nb][e] = seen ? s[nb][e] * a.scale : -INFINITY;
+          s[nb][e] = seen ? s[nb][e] * a.scale - slope * float(pi - j) : -INFINITY;
         }
         mx0 = fmaxf(mx0, fmaxf(s[nb][0], s[nb][1]));
         mx1 = fmaxf(mx1, fmaxf(s[nb][2], s[nb][3]));
@@ -422,7 +509,8 @@ __global__ void __launch_bounds__(128) softmax_attention_mma_kernel(const Softma
     }
     return;
   }
-  const float f0 = a.out_scale / l_run[0], f1 = a.out_scale / l_run[1];
+  const float f0 = a.out_scale / l_run[0] * (g < nr ? smax_gate(a.gate, a.ld_gate, r0 + g, h) : 1.0f);
+  const float f1 = a.out_scale / l_run[1] * (g + 8 < nr ? smax_gate(a.gate, a.ld_gate, r0 + g + 8, h) : 1.0f);
   bf16* out0 = a.out + size_t(r0 + g) * a.ld_out + h * D + part * DVW + 2 * t;
   bf16* out1 = out0 + size_t(8) * a.ld_out;
 #pragma unroll
@@ -499,6 +587,15 @@ __global__ void __launch_bounds__(kSdecWarps * 32) softmax_attention_decode_kern
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[mb][e] = 0.0f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};  // heads 2t, 2t + 1
+  float slope0 = 0.0f, slope1 = 0.0f;
+  if (a.slopes) {
+    slope0 = 2 * t < rep ? a.slopes[kvh * rep + 2 * t] : 0.0f;
+    slope1 = 2 * t + 1 < rep ? a.slopes[kvh * rep + 2 * t + 1] : 0.0f;
+  }
+  if (a.sink && warp == 0 && blockIdx.z == 0) {  // (the first warp of the first split carries the sink; its eight lanes of a head are added at the end)
+    if (2 * t < rep) m_run[0] = a.sink[kvh * rep + 2 * t], l_run[0] = g == 0 ? 1.0f : 0.0f;
+    if (2 * t + 1 < rep) m_run[1] = a.sink[kvh * rep + 2 * t + 1], l_run[1] = g == 0 ? 1.0f : 0.0f;
+  }
 
   if (n_key_tiles > 0) load_tile(0, 0);
   for (int it = 0; it < n_key_tiles; ++it) {
@@ -527,10 +624,10 @@ __global__ void __launch_bounds__(kSdecWarps * 32) softmax_attention_decode_kern
       // c[0], c[1]: key j0 + g, heads 2t, 2t + 1;  c[2], c[3]: key j0 + g + 8
       const int ja = j0 + g, jb = j0 + g + 8;
       const bool sa_ = ja <= pos && (a.window <= 0 || pos - ja < a.window), sb_ = jb <= pos && (a.window <= 0 || pos - jb < a.window);
-      c[0] = sa_ ? c[0] * a.scale : -INFINITY;
-      c[1] = sa_ ? c[1] * a.scale : -INFINITY;
-      c[2] = sb_ ? c[2] * a.scale : -INFINITY;
-      c[3] = sb_ ? c[3] * a.scale : -INFINITY;
+      c[0] = sa_ ? c[0] * a.scale - slope0 * float(pos - ja) : -INFINITY;
+      c[1] = sa_ ? c[1] * a.scale - slope1 * float(pos - ja) : -INFINITY;
+      c[2] = sb_ ? c[2] * a.scale - slope0 * float(pos - jb) : -INFINITY;
+      c[3] = sb_ ? c[3] * a.scale - slope1 * float(pos - jb) : -INFINITY;
       float mx0 = fmaxf(c[0], c[2]), mx1 = fmaxf(c[1], c[3]);
 #pragma unroll
       for (int sh = 4; sh < 32; sh <<= 1) {
@@ -612,7 +709,7 @@ __global__ void __launch_bounds__(kSdecWarps * 32) softmax_attention_decode_kern
         a.part_ml[base * 2 + 1] = L;
       }
     } else {
-      a.out[size_t(row) * a.ld_out + h * D + col] = __float2bfloat16_rn(acc * a.out_scale / L);
+      a.out[size_t(row) * a.ld_out + h * D + col] = __float2bfloat16_rn(acc * a.out_scale / L * smax_gate(a.gate, a.ld_gate, row, h));
     }
   }
 }
@@ -630,6 +727,7 @@ __global__ void __launch_bounds__(128) softmax_attention_merge_kernel(const Soft
     const float* ml = a.part_ml + ((size_t(z) * a.rows + row) * a.heads + h) * 2;
     if (ml[0] != -INFINITY) L += __expf(ml[0] - M) * ml[1];
   }
+  const float gate = smax_gate(a.gate, a.ld_gate, row, h);
   for (int c = lane; c < D; c += 32) {
     float acc = 0.0f;
     for (int z = 0; z < a.splits; ++z) {
@@ -637,7 +735,7 @@ __global__ void __launch_bounds__(128) softmax_attention_merge_kernel(const Soft
       const float mz = a.part_ml[base * 2];
       if (mz != -INFINITY) acc = fmaf(__expf(mz - M), a.part_o[base * D + c], acc);
     }
-    a.out[size_t(row) * a.ld_out + h * D + c] = __float2bfloat16_rn(acc * a.out_scale / L);
+    a.out[size_t(row) * a.ld_out + h * D + c] = __float2bfloat16_rn(acc * a.out_scale / L * gate);
   }
 }
 

@@ -28,14 +28,17 @@ from . import params as params_lib
 from .maxengine import ExistingPrefix, MaxEngine, ResultTokens  # noqa: F401  (same result types)
 
 _MIXERS = {"window_sigmoid": _lib.MIXER_WINDOW_SIGMOID, "composite": _lib.MIXER_COMPOSITE}
-_NORMS = {"out_gain": _lib.NORM_OUT_GAIN, "sandwich": _lib.NORM_SANDWICH}
-_FF_KINDS = {"none": _lib.FF_GELU_GATED, "gelu": _lib.FF_GELU_GATED, "clamped": _lib.FF_CLAMPED_GATED, "moe": _lib.FF_MOE}
-_RECURRENCES = {"gla": _lib.REC_GLA, "mlstm": _lib.REC_MLSTM}
+_NORMS = {"out_gain": _lib.NORM_OUT_GAIN, "sandwich": _lib.NORM_SANDWICH, "parallel": _lib.NORM_PARALLEL}
+_FF_KINDS = {"none": _lib.FF_GELU_GATED, "gelu": _lib.FF_GELU_GATED, "clamped": _lib.FF_CLAMPED_GATED, "moe": _lib.FF_MOE, "relu2": _lib.FF_RELU2}
+_RECURRENCES = {"gla": _lib.REC_GLA, "mlstm": _lib.REC_MLSTM, "delta": _lib.REC_DELTA}
 QUERY_TILE_ROWS = 16  # rows of one query tile of the attention kernels (csrc/window_attention_mma.cuh, csrc/softmax_attention.cuh)
 
 _LAYER_MATS = ("wqkv", "wo", "w_gate_up", "w_down", "w_in")
-_LAYER_VECS = ("bqkv", "q_norm", "k_norm", "dist_bias", "head_bias", "talk", "norm1", "norm1b", "norm2", "norm2b", "add_vector", "b_in", "bo")
-_ATTN_VECS = ("rot_freq",)
+_LAYER_VECS = ("bqkv", "q_norm", "k_norm", "dist_bias", "head_bias", "talk", "norm1", "norm1b", "norm2", "norm2b", "add_vector", "b_in", "bo",
+               "conv1", "conv2")
+_ATTN_VECS = ("q_norm", "k_norm", "slopes", "sink")
+_LATENT_MATS = ("w_uq", "w_uk_t", "w_uv")
+_LATENT_VECS = ("q_norm", "kv_norm", "sink")
 _REC_VECS = ("decay_up_t", "decay_bias", "gate_bias", "out_norm")
 _MOE_MATS = ("w_router", "w_gate_up", "w_down", "shared_gate_up", "shared_down")
 _MOE_VECS = ("correction",)
@@ -51,6 +54,10 @@ def design_module(config):
     from . import gugidra
 
     return gugidra
+  if config.decoder_block == "ginodra":
+    from . import ginodra
+
+    return ginodra
   raise ValueError(f"decoder_block={config.decoder_block!r} is not a layered design")
 
 
@@ -93,13 +100,17 @@ class LayeredParams:
     self.final_gain, self.embed_scale = float(plan["final_gain"]), float(plan["embed_scale"])
     self.final_norm = vec(plan.get("final_norm"))
     self.logit_softcap = float(plan.get("logit_softcap") or 0.0)
+    self.logit_scale = float(plan.get("logit_scale") or 1.0)
+    self.norm_groups = int(plan.get("norm_groups") or 0)
     self.layers = []
     for lp in plan["layers"]:
       d = pack(lp, _LAYER_MATS, _LAYER_VECS)
       if d.get("attn"):
-        d["attn"] = dict(d["attn"])
-        for k in _ATTN_VECS:  # (the rotation's frequencies stay float64)
-          d["attn"][k] = put(d["attn"].get(k), torch.float64)
+        d["attn"] = pack(d["attn"], (), _ATTN_VECS)
+        d["attn"]["rot_freq"] = put(d["attn"].get("rot_freq"), torch.float64)  # (the rotation's frequencies stay float64)
+      if d.get("latent"):
+        d["latent"] = pack(d["latent"], _LATENT_MATS, _LATENT_VECS)
+        d["latent"]["rot_freq"] = put(d["latent"].get("rot_freq"), torch.float64)
       if d.get("rec"):
         d["rec"] = pack(d["rec"], (), _REC_VECS)
       if d.get("moe"):
@@ -224,15 +235,34 @@ class LayeredEngine(MaxEngine):
         d.k_pages, d.v_pages = kp.data_ptr(), vp.data_ptr()
       else:
         d.n_in, d.add_embedding, d.ff_limit = int(l["n_in"]), int(l.get("add_embedding", 0)), float(l.get("ff_limit", 0.0))
-        for k in ("norm1", "norm1b", "norm2", "norm2b", "add_vector", "w_in", "b_in", "bo"):
+        for k in ("norm1", "norm1b", "norm2", "norm2b", "add_vector", "w_in", "b_in", "bo", "conv1", "conv2"):
           setattr(d, k, ptr(l.get(k)))
-        a, r, m = l.get("attn"), l.get("rec"), l.get("moe")
+        a, r, m, lat = l.get("attn"), l.get("rec"), l.get("moe"), l.get("latent")
+        d.conv_taps, d.residual_mult = int(l.get("conv_taps", 0)), float(l.get("residual_mult", 1.0))
+        if d.conv_taps > 1:  # the ring of a sequence's last normed rows, per state slot
+          states += (torch.zeros(slots, d.conv_taps - 1, int(cfg.emb_dim), dtype=torch.float32, device=dev),)
+          d.conv_state = states[-1].data_ptr()
         if a:
-          kp, vp = pools(a["kv_heads"], a["dim"], a["vdim"])
-          for k in ("heads", "kv_heads", "dim", "vdim", "window", "rot_dims", "values_are_keys"):
-            setattr(d.attn, k, int(a[k]))
+          if a.get("kv_from") is not None:  # the pools of an earlier layer, read as that layer writes them
+            kp, vp = self._pools[int(a["kv_from"])]
+            self._pools.append(())
+          else:
+            kp, vp = pools(a["kv_heads"], a["dim"], a["vdim"])
+          for k in ("heads", "kv_heads", "dim", "vdim", "window", "rot_dims", "values_are_keys", "rot_half", "shared_kv", "head_gate"):
+            setattr(d.attn, k, int(a.get(k, 0)))
           d.attn.scale, d.attn.out_scale = float(a["scale"]), float(a["out_scale"])
           d.attn.rot_freq, d.attn.k_pages, d.attn.v_pages = ptr(a["rot_freq"]), kp.data_ptr(), vp.data_ptr()
+          for k in _ATTN_VECS:
+            setattr(d.attn, k, ptr(a.get(k)))
+        elif lat:
+          dl = int(lat["kv_rank"]) + int(lat["rot_dim"])
+          kp = torch.zeros(1, pm.num_pages, pm.tokens_per_page, dl, dtype=ct, device=dev)  # [latent | rotated key part] per token
+          self._pools.append((kp, kp))
+          for k in ("heads", "dim", "rot_dim", "vdim", "q_rank", "kv_rank", "rot_half"):
+            setattr(d.latent, k, int(lat[k]))
+          d.latent.scale, d.latent.pages = float(lat["scale"]), kp.data_ptr()
+          for k in ("rot_freq",) + _LATENT_MATS + _LATENT_VECS:
+            setattr(d.latent, k, ptr(lat.get(k)))
         else:
           self._pools.append(())
         if r:
@@ -241,15 +271,17 @@ class LayeredEngine(MaxEngine):
             setattr(d.rec, k, int(r[k]))
           for k in ("q_scale", "tau", "gate_cap", "denom_eps", "out_scale"):
             setattr(d.rec, k, float(r[k]))
+          d.rec.decay_rate, d.rec.key_eps = float(r.get("decay_rate", 0.0)), float(r.get("key_eps", 0.0))
           for k in ("decay_up_t", "decay_bias", "gate_bias", "out_norm"):
             setattr(d.rec, k, ptr(r.get(k)))
           H, dk, dv = int(r["heads"]), int(r["dim"]), int(r["vdim"])
           f32 = torch.float32
-          states = (torch.zeros(slots, H, dv, dk, dtype=f32, device=dev),)
-          d.rec.state_s = states[0].data_ptr()
+          rec_states = (torch.zeros(slots, H, dv, dk, dtype=f32, device=dev),)
+          d.rec.state_s = rec_states[0].data_ptr()
           if r["kind"] == "mlstm":
-            states += (torch.zeros(slots, H, dk, dtype=f32, device=dev), torch.zeros(slots, H, dtype=f32, device=dev))
-            d.rec.state_n, d.rec.state_m = states[1].data_ptr(), states[2].data_ptr()
+            rec_states += (torch.zeros(slots, H, dk, dtype=f32, device=dev), torch.zeros(slots, H, dtype=f32, device=dev))
+            d.rec.state_n, d.rec.state_m = rec_states[1].data_ptr(), rec_states[2].data_ptr()
+          states += rec_states
         if m:
           for k in ("experts", "top", "groups", "keep_groups", "ff", "shared_ff"):
             setattr(d.moe, k, int(m[k]))
@@ -260,12 +292,17 @@ class LayeredEngine(MaxEngine):
         setattr(d, k, ptr(l.get(k)))
       self._states.append(states)
     self._needs_runs = any(l["mixer"] == "composite" for l in lp.layers)
+    self._pool_tensors = []  # every page pool once (a pool that serves two roles or two layers is one tensor)
+    for pool in self._pools:
+      for t in pool:
+        if not any(t is u for u in self._pool_tensors):
+          self._pool_tensors.append(t)
     c = _lib.LayeredConfig(
         num_layers=len(lp.layers), width=int(cfg.emb_dim), vocab=int(cfg.vocab_size), float32=1 if lp.float32 else 0,
         max_rows=self._max_rows, max_want=self._max_rows, num_groups=slots, num_pages=pm.num_pages,
         tokens_per_page=pm.tokens_per_page, max_pages_per_group=pm.max_pages_per_group, eps=float(cfg.normalization_layer_epsilon),
         embed_scale=lp.embed_scale, final_gain=lp.final_gain, embedding=lp.embedding.data_ptr(), head=lp.head.data_ptr(),
-        final_norm=ptr(lp.final_norm), logit_softcap=lp.logit_softcap)
+        final_norm=ptr(lp.final_norm), logit_softcap=lp.logit_softcap, norm_groups=lp.norm_groups, logit_scale=lp.logit_scale)
     _lib.check(self.lib.mtx_layered_create(ctypes.byref(c), descs, ctypes.byref(self._handle)))
     ws = int(self.lib.mtx_layered_workspace_bytes(self._handle))
     self._ws = torch.empty(ws + 1024, dtype=torch.uint8, device=dev)
@@ -290,7 +327,7 @@ class LayeredEngine(MaxEngine):
     self._logits = torch.zeros(B, 1, V, dtype=torch.float32, device=self.device)
     self._state = {
         "logits": self._logits,
-        "cache": {"key_pages": [p[0] for p in self._pools if p], "value_pages": [p[1] for p in self._pools if p],
+        "cache": {"key_pages": [p[0] for p in self._pools if p], "value_pages": [p[1] for p in self._pools if p and p[1] is not p[0]],
                   "recurrent_state": [t for st in self._states for t in st]},
         "next_pos": self._next_pos,
         "generated_tokens": self._generated,
@@ -480,12 +517,11 @@ class LayeredEngine(MaxEngine):
       self._next_pos[slot].fill_(n)
     self.page_state = ps
     self._upload_page_map()
-    for pool in self._pools:
-      for buf in pool:
-        flat = buf.view(-1)
-        for lo in range(0, flat.numel(), 1 << 26):
-          n = min(1 << 26, flat.numel() - lo)
-          flat[lo : lo + n] = torch.randn(n, device=self.device, generator=g).to(buf.dtype)
+    for buf in self._pool_tensors:
+      flat = buf.view(-1)
+      for lo in range(0, flat.numel(), 1 << 26):
+        n = min(1 << 26, flat.numel() - lo)
+        flat[lo : lo + n] = torch.randn(n, device=self.device, generator=g).to(buf.dtype)
     for st in self._states:
       for t in st:
         t.copy_(torch.randn(t.shape, device=self.device, generator=g) * 0.1)

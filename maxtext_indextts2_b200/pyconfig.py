@@ -36,8 +36,8 @@ _VALID_SAMPLING = ("greedy", "weighted", "nucleus", "topk")
 _VALID_AXIS_ORDER = ("0,1,2,3", "0,2,1,3")
 # Designs whose layers are listed one by one (`layer_specs`) and run on the layered engine (layered_engine.py), keyed by
 # decoder_block; ARCHITECTURES maps the "architecture" of a model folder's config.json to the block.
-LAYERED_BLOCKS = ("kifusun", "gugidra")
-ARCHITECTURES = {"Kifusun": "kifusun", "Gugidra": "gugidra"}
+LAYERED_BLOCKS = ("kifusun", "gugidra", "ginodra")
+ARCHITECTURES = {"Kifusun": "kifusun", "Gugidra": "gugidra", "Ginodra": "ginodra"}
 
 
 def _string_to_bool(s: str) -> bool:
@@ -128,6 +128,14 @@ def _validate_layered(keys: dict) -> None:
     gugidra.validate_layer_specs(keys["layer_specs"], keys["layer_loop"])
   elif keys["layer_loop"]:
     raise ValueError("layer_loop belongs to designs that repeat a span of layers")
+  if keys["decoder_block"] == "ginodra":
+    from . import ginodra
+
+    ginodra.validate_layer_specs(keys["layer_specs"])
+    if int(keys["norm_groups"]) < 1 or int(keys["emb_dim"]) % int(keys["norm_groups"]):
+      raise ValueError("norm_groups must divide the width")
+    if int(keys["input_conv_taps"]) < 1:
+      raise ValueError("input_conv_taps must be positive")
 
 
 def _validate(keys: dict) -> None:
@@ -292,6 +300,10 @@ def from_model_dict(model: dict, **overrides) -> HyperParameters:
     from . import gugidra
 
     keys = gugidra.config_keys(model)
+  elif block == "ginodra":
+    from . import ginodra
+
+    keys = ginodra.config_keys(model)
   keys.update(decoder_block=block, attention="paged", scan_layers=False, weight_dtype="bfloat16")
   keys.update(overrides)
   if "max_prefill_predict_length" not in overrides:  # any prompt that fits the sequence
