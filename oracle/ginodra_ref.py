@@ -84,9 +84,10 @@ def window_mask(T: int, window: Optional[int]):
   return m
 
 
-def windowed_attention(h, p: Dict[str, np.ndarray], spec: dict, eps: float, shared_kv=None):
+def windowed_attention(h, p: Dict[str, np.ndarray], spec: dict, eps: float, shared_kv=None, fault: Optional[dict] = None):
   """Grouped-query softmax attention with per-head q/k norm, a linear distance penalty and a sliding window.  Returns the mixer's
-  output and the (normed keys, values) it used, which a later layer may take over (`shared_kv`)."""
+  output and the (normed keys, values) it used, which a later layer may take over (`shared_kv`).  `fault` (tests of the tests):
+  {"window_shift": n} widens the window by n keys."""
   T = h.shape[0]
   H, G, d, dv = int(spec["heads"]), int(spec["kv_heads"]), int(spec["dim"]), int(spec["vdim"])
   q = rms_unit((h @ p["q"].T).reshape(T, H, d), eps) * p["q.norm"]
@@ -97,7 +98,7 @@ def windowed_attention(h, p: Dict[str, np.ndarray], spec: dict, eps: float, shar
     k, v = shared_kv
   gate = sigmoid(h @ p["g"].T)  # [T, H]
   slopes = distance_slopes(H)
-  mask = window_mask(T, int(spec["mask"]["size"]) if spec.get("mask") else None)
+  mask = window_mask(T, int(spec["mask"]["size"]) + int((fault or {}).get("window_shift", 0)) if spec.get("mask") else None)
   dist = (np.arange(T)[:, None] - np.arange(T)[None, :]).astype(np.float64)
   out = np.zeros((T, H, dv))
   for hd in range(H):
@@ -107,9 +108,10 @@ def windowed_attention(h, p: Dict[str, np.ndarray], spec: dict, eps: float, shar
   return out.reshape(T, H * dv) @ p["o"].T, (k, v)
 
 
-def latent_attention(h, p: Dict[str, np.ndarray], spec: dict, eps: float):
+def latent_attention(h, p: Dict[str, np.ndarray], spec: dict, eps: float, fault: Optional[dict] = None):
   """Queries through a normed latent; keys and values expanded from a normed latent c; one rotated key part shared by the heads;
-  causal softmax whose denominator also holds exp(sink) per head; a sigmoid gate per head."""
+  causal softmax whose denominator also holds exp(sink) per head; a sigmoid gate per head.  `fault` (tests of the tests):
+  {"horizon": n} hides keys more than n positions back, {"no_sink": True} leaves the sink out."""
   T = h.shape[0]
   H, d, dr, dv, rank = int(spec["heads"]), int(spec["dim"]), int(spec["rot_dim"]), int(spec["vdim"]), int(spec["kv_rank"])
   pos = np.arange(T)
@@ -123,11 +125,12 @@ def latent_attention(h, p: Dict[str, np.ndarray], spec: dict, eps: float):
   k_plain = (c @ p["uk"].T).reshape(T, H, d)
   v = (c @ p["uv"].T).reshape(T, H, dv)
   gate = sigmoid(h @ p["g"].T)
-  mask = window_mask(T, None)
+  fault = fault or {}
+  mask = window_mask(T, int(fault["horizon"]) + 1 if "horizon" in fault else None)
   out = np.zeros((T, H, dv))
   for hd in range(H):
     s = (q_plain[:, hd] @ k_plain[:, hd].T + q_rot[:, hd] @ k_rot.T) * float(spec["scale"])
-    out[:, hd] = (softmax_rows(s, mask, sink=float(p["sink"][hd])) @ v[:, hd]) * gate[:, hd : hd + 1]
+    out[:, hd] = (softmax_rows(s, mask, sink=None if fault.get("no_sink") else float(p["sink"][hd])) @ v[:, hd]) * gate[:, hd : hd + 1]
   return out.reshape(T, H * dv) @ p["o"].T
 
 
@@ -165,7 +168,7 @@ def sub(tensors: Dict[str, np.ndarray], prefix: str) -> Dict[str, np.ndarray]:
   return {k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)}
 
 
-def forward(model: dict, tensors: Dict[str, np.ndarray], tokens: List[int], return_layers: bool = False):
+def forward(model: dict, tensors: Dict[str, np.ndarray], tokens: List[int], return_layers: bool = False, fault: Optional[dict] = None):
   """Logits [T, vocab] of one sequence (and the residual stream after every layer, [L, T, E])."""
   eps, groups = float(model["norm"]["eps"]), int(model["norm"]["groups"])
   m = float(model["residual_mult"])
@@ -178,9 +181,9 @@ def forward(model: dict, tensors: Dict[str, np.ndarray], tokens: List[int], retu
     spec, p = layer["mixer"], sub(tensors, pre + "mix.")
     if layer["type"] == "attention":
       src = spec.get("kv_from")
-      y, kept[i] = windowed_attention(hm, p, spec, eps, kept[int(src)] if src is not None else None)
+      y, kept[i] = windowed_attention(hm, p, spec, eps, kept[int(src)] if src is not None else None, fault)
     elif layer["type"] == "latent_attention":
-      y = latent_attention(hm, p, spec, eps)
+      y = latent_attention(hm, p, spec, eps, fault)
     elif layer["type"] == "general_delta":
       y = general_delta(hm, p, spec, eps)
     else:
