@@ -66,7 +66,7 @@ def parse_args():
   ap.add_argument("--no-verify", action="store_true", help="skip the oracle check of one step of the timed state")
   ap.add_argument("--prompt-len", type=int, default=4000, help="--mode prefill: prompt tokens (BASELINE configs[3]: 4000 of P = 4096)")
   ap.add_argument("--size", default="all", help="--mode layered: one of the sizes of LAYERED_SIZES, or all")
-  ap.add_argument("--design", default="kifusun", choices=["kifusun", "gugidra"], help="--mode layered: the layered design that is measured beside gemma3")
+  ap.add_argument("--design", default="kifusun", choices=["kifusun", "gugidra", "ginodra"], help="--mode layered: the layered design that is measured beside gemma3")
   ap.add_argument("--mode", default="batch", choices=["batch", "vocab-parallel", "prefill", "layered"],
                   help="batch: request-batch partitioned, no collective (default); vocab-parallel: every GPU decodes the same --batch slots, "
                        "the logits projection is sharded over the GPUs and one NCCL all-gather carries the per-shard candidates")
@@ -614,7 +614,7 @@ def run_layered(args):
   """--mode layered: prefill and decode throughput of a layered design (--design) on the layered engine beside the gemma3 block
   (the closest existing model: softmax attention with rotary positions and grouped key heads, norms before and after every
   sublayer, gated feed-forward) at equal layer sizes, both through MaxEngine.  One JSON line per size."""
-  from maxtext_indextts2_b200 import gugidra, kifusun, maxengine, pyconfig
+  from maxtext_indextts2_b200 import ginodra, gugidra, kifusun, maxengine, pyconfig
 
   D = args.design  # (the keys of the output line carry the design's name)
   names = list(LAYERED_SIZES) if args.size == "all" else [args.size]
@@ -630,6 +630,18 @@ def run_layered(args):
     if D == "kifusun":
       layers = [kifusun.attention_layer(z["heads"], z["kv_heads"], z["dim"], z["dim"], z["window"], ff=z["ff"], bias_max=float(z["window"])) for _ in range(L)]
       model = kifusun.model_dict(z["width"], z["vocab"], layers, embed_scale=1.0)
+    elif D == "ginodra":
+      # Ginodra at the same sizes, one layer of each kind: a delta-rule layer (gemma3's heads, half the key channels per head), a
+      # windowed attention with gemma3's heads and window, a second one that reads the first one's cache, and a latent attention
+      # (gemma3's query heads; cached rows of 3/4 latent + 1/4 rotated part, as wide as two of gemma3's key heads); every layer
+      # with a dense feed-forward of gemma3's size
+      H, G, d, F, W = z["heads"], z["kv_heads"], z["dim"], z["ff"], z["window"]
+      row = min(256, 2 * d)
+      layers = [ginodra.delta_layer(H, d // 2, mlp=ginodra.dense_ff(F), rank=64),
+                ginodra.attention_layer(H, G, d, window=W, mlp=ginodra.dense_ff(F)),
+                ginodra.attention_layer(H, G, d, window=W, kv_from=1, mlp=ginodra.dense_ff(F)),
+                ginodra.latent_layer(H, d // 2, row // 4, d // 2, z["width"] // 2, row - row // 4, mlp=ginodra.dense_ff(F))][:L]
+      model = ginodra.model_dict(z["width"], z["vocab"], layers, groups=2, taps=4)
     else:
       # Gugidra at the same sizes: attention + mLSTM layers and GLA layers in turn; the attention has gemma3's heads (no window: the
       # design has none), the recurrences half as many key channels per head; dense feed-forwards of gemma3's size in turn with

@@ -178,16 +178,50 @@ __global__ void softcap_kernel(float* z, float cap, long long total) {
     z[i] = cap * tanhf(z[i] / cap);
 }
 
+template <typename T>
+struct InputConvArgs {
+  const float* h;        // [rows, width] the normed rows of this step
+  const float* w1;       // [taps, width]: tap j multiplies the row taps - 1 - j steps back (the last tap the row itself)
+  const float* w2;       // the same for the second output, or null
+  float* state;          // [slots, taps - 1, width]: the normed row of position p of a sequence at index p % (taps - 1)
+  T* out1;               // [rows, width] h + conv1(h)
+  T* out2;               // [rows, width] h + conv2(h) (w2 null: h itself)
+  const int* group;
+  const int* pos;
+  int rows, width, taps;
+};
+
 // one CTA of eight warps per row.  A group's sum of squares is added in a fixed order: by one warp when there are eight groups or
 // more, else by 8 / groups warps whose partial sums meet in shared memory.
+// FUSED (steps in which every row is a single token of its own sequence): the row's normed values do not go to the plane h but
+// straight through the input convolutions (the earlier rows come from the sequence's ring) and into the ring.  The arithmetic is
+// that of input_conv_kernel, value by value, so a position's result does not depend on which of the two paths served it.
+template <typename T, bool FUSED>
 __global__ void __launch_bounds__(256) group_norm_step_kernel(const float* y, float mult, float* x, const float* w, float eps, float* h, int width,
-                                                              int groups) {
+                                                              int groups, const InputConvArgs<T> cv) {
   __shared__ float red[8];
   griddep_wait();
   const int r = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gs = width / groups;
   float* xr = x + size_t(r) * width;
   const float* yr = y ? y + size_t(r) * width : nullptr;
   float* hr = h + size_t(r) * width;
+  const int p = FUSED ? cv.pos[r] : 0, grp = FUSED ? cv.group[r] : 0, ring = cv.taps - 1;
+  auto emit = [&](int c, float hv) {
+    if constexpr (!FUSED) {
+      hr[c] = hv;
+    } else {
+      const int W = width;
+      float s1 = hv * cv.w1[size_t(ring) * W + c], s2 = cv.w2 ? hv * cv.w2[size_t(ring) * W + c] : 0.0f;
+      for (int back = 1; back <= ring && back <= p; ++back) {
+        const float v = cv.state[(size_t(grp) * ring + (p - back) % ring) * W + c];
+        s1 = fmaf(v, cv.w1[size_t(ring - back) * W + c], s1);
+        if (cv.w2) s2 = fmaf(v, cv.w2[size_t(ring - back) * W + c], s2);
+      }
+      cv.out1[size_t(r) * W + c] = to_act<T>(hv + s1);
+      cv.out2[size_t(r) * W + c] = to_act<T>(hv + s2);
+      if (ring > 0) cv.state[(size_t(grp) * ring + p % ring) * W + c] = hv;  // (the slot of position p - ring, read just above by this thread)
+    }
+  };
   if (groups >= 8) {
     for (int g = warp; g < groups; g += 8) {
       const int base = g * gs;
@@ -203,7 +237,7 @@ __global__ void __launch_bounds__(256) group_norm_step_kernel(const float* y, fl
       ss = warp_sum(ss);
       const float f = 1.0f / sqrtf(ss / float(gs) + eps);
       if (w)
-        for (int c = lane; c < gs; c += 32) hr[base + c] = xr[base + c] * f * w[base + c];
+        for (int c = lane; c < gs; c += 32) emit(base + c, xr[base + c] * f * w[base + c]);
     }
     return;
   }
@@ -228,7 +262,7 @@ __global__ void __launch_bounds__(256) group_norm_step_kernel(const float* y, fl
   float tot = 0.0f;
   for (int i = 0; i < wpg; ++i) tot += red[g * wpg + i];
   const float f = 1.0f / sqrtf(tot / float(gs) + eps);
-  for (int c = wi * 32 + lane; c < gs; c += wpg * 32) hr[base + c] = xr[base + c] * f * w[base + c];
+  for (int c = wi * 32 + lane; c < gs; c += wpg * 32) emit(base + c, xr[base + c] * f * w[base + c]);
 }
 
 template <typename T>
@@ -254,18 +288,6 @@ __global__ void logit_post_kernel(float* z, float scale, float cap, long long to
   }
 }
 
-template <typename T>
-struct InputConvArgs {
-  const float* h;        // [rows, width] the normed rows of this step
-  const float* w1;       // [taps, width]: tap j multiplies the row taps - 1 - j steps back (the last tap the row itself)
-  const float* w2;       // the same for the second output, or null
-  const float* state;    // [slots, taps - 1, width]: the normed row of position p of a sequence at index p % (taps - 1)
-  T* out1;               // [rows, width] h + conv1(h)
-  T* out2;               // [rows, width] h + conv2(h) (w2 null: h itself)
-  const int* group;
-  const int* pos;
-  int rows, width, taps;
-};
 
 // one CTA per row.  The row `back` steps before row r is row r - back of the batch when that is the same sequence's previous
 // position (rows of a run are consecutive), a row of the state when the run began later, and zero before the sequence's start.

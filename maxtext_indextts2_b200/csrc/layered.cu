@@ -597,19 +597,20 @@ int launch_softmax_mma_any(const SoftmaxAttnArgs<bf16>& sa, const SoftmaxMmaPlan
 
 template <int D16>
 int launch_softmax_decode_t(const SoftmaxAttnArgs<bf16>& sa, cudaStream_t st) {
-  const size_t smem = softmax_decode_smem_bytes(sa.dim);
+  const size_t smem = softmax_decode_smem_bytes(sa.dim, sa.k_pages == sa.v_pages);
   static size_t have = 0;  // per instantiation
   if (smem > 48 * 1024 && smem > have) {
     MTX_CUDA(cudaFuncSetAttribute(softmax_attention_decode_kernel<D16>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
     have = smem;
   }
-  return launch(softmax_attention_decode_kernel<D16>, dim3(sa.rows, sa.kv_heads, sa.splits), dim3(kSdecWarps * 32), smem, st, sa);
+  const int chunks = (sa.heads / sa.kv_heads + 7) / 8;
+  return launch(softmax_attention_decode_kernel<D16>, dim3(sa.rows, sa.kv_heads * chunks, sa.splits), dim3(kSdecWarps * 32), smem, st, sa);
 }
 
 // a step of single tokens (every row its own tile and sequence): the transposed kernel, its keys cut into splits until every SM
 // has about three CTAs (what its shared memory lets an SM hold)
 int launch_softmax_decode(mtx_layered* e, SoftmaxAttnArgs<bf16> sa, int d16, cudaStream_t st) {
-  const long long ctas = (long long)sa.rows * sa.kv_heads;
+  const long long ctas = (long long)sa.rows * sa.kv_heads * ((sa.heads / sa.kv_heads + 7) / 8);
   long long sp = (3LL * e->num_sms + ctas - 1) / ctas;
   sa.splits = int(sp > 4 ? 4 : (sp < 1 ? 1 : sp));
   if (size_t(sa.splits) * sa.rows > e->attn_part_rows) sa.splits = 1;
@@ -671,7 +672,7 @@ int run_softmax_attention(mtx_layered* e, SoftmaxAttnArgs<T>& sa, const mtx_ragg
     const SoftmaxMmaPlan plan = softmax_mma_plan(sa.heads, sa.kv_heads, sa.dim, sa.vdim);
     static const int decode_arm = env_int("MTX_SOFTMAX_DECODE", 1);
     if (plan.ok && use_softmax_mma() && sa.ld_out % 2 == 0) {
-      if (b.n_tiles == sa.rows && sa.heads / sa.kv_heads <= 8 && decode_arm) MTX_TRY(launch_softmax_decode(e, sa, plan.d16, st));
+      if (b.n_tiles == sa.rows && decode_arm) MTX_TRY(launch_softmax_decode(e, sa, plan.d16, st));
       else MTX_TRY(launch_softmax_mma(e, sa, plan, b.n_tiles, b.n_tiles == sa.rows, st));
       done = true;
     }
@@ -900,11 +901,44 @@ ParallelCols parallel_cols(const mtx_layer_desc& l) {
   return pc;
 }
 
-// x += mult * y (y null: no update), then h = gnorm(x) with the weight of layer `next` (none after the last layer)
-int group_norm_step(mtx_layered* e, const float* y, float mult, int next, int rows, cudaStream_t st) {
-  const float* w = next < e->cfg.num_layers ? e->layers[next].norm1 : nullptr;
+// every row of the step is a single token of its own sequence: the norm, the input convolutions and the ring update are one kernel
+bool single_token_rows(const mtx_ragged_batch& b) {
+  static int on = env_int("MTX_FUSED_NORM_CONV", 1);
+  return on != 0 && b.n_runs == b.rows;
+}
+
+template <typename T>
+InputConvArgs<T> input_conv_args(mtx_layered* e, const mtx_layer_desc& l, const mtx_ragged_batch& b) {
+  InputConvArgs<T> ca;
+  memset(&ca, 0, sizeof(ca));
+  ca.h = e->h;
+  ca.w1 = l.conv1;
+  ca.w2 = l.ff > 0 ? l.conv2 : nullptr;
+  ca.state = l.conv_state;
+  ca.out1 = static_cast<T*>(e->xa);  // the mixer's input
+  ca.out2 = static_cast<T*>(e->xb);  // the feed-forward's input
+  ca.group = b.group;
+  ca.pos = b.pos;
+  ca.rows = b.rows;
+  ca.width = e->cfg.width;
+  ca.taps = l.conv_taps;
+  return ca;
+}
+
+// x += mult * y (y null: no update), then h = gnorm(x) with the weight of layer `next` (none after the last layer); in steps of
+// single tokens also that layer's input convolutions
+template <typename T>
+int group_norm_step(mtx_layered* e, const float* y, float mult, int next, const mtx_ragged_batch& b, cudaStream_t st) {
+  const bool last = next >= e->cfg.num_layers;
+  const float* w = last ? nullptr : e->layers[next].norm1;
   if (!y && !w) return MTX_OK;
-  return launch(group_norm_step_kernel, dim3(rows), dim3(256), 0, st, y, mult, e->x, w, e->cfg.eps, e->h, e->cfg.width, e->cfg.norm_groups);
+  const mtx_layered_config& c = e->cfg;
+  if (!last && single_token_rows(b))
+    return launch(group_norm_step_kernel<T, true>, dim3(b.rows), dim3(256), 0, st, y, mult, e->x, w, c.eps, e->h, c.width, c.norm_groups,
+                  input_conv_args<T>(e, e->layers[next], b));
+  InputConvArgs<T> none;
+  memset(&none, 0, sizeof(none));
+  return launch(group_norm_step_kernel<T, false>, dim3(b.rows), dim3(256), 0, st, y, mult, e->x, w, c.eps, e->h, c.width, c.norm_groups, none);
 }
 
 // a MTX_NORM_PARALLEL layer; h holds gnorm(x, norm1) on entry
@@ -918,23 +952,12 @@ int parallel_layer(mtx_layered* e, int li, const mtx_ragged_batch& b, cudaStream
   const ParallelCols pc = parallel_cols(l);
   const int n_in = l.n_in, k_cat = pc.k_mix + l.ff;
   T* cat = static_cast<T*>(e->attn);  // [rows, k_cat]: the mixer's heads, then the feed-forward's hidden units
-  InputConvArgs<T> ca;
-  memset(&ca, 0, sizeof(ca));
-  ca.h = e->h;
-  ca.w1 = l.conv1;
-  ca.w2 = l.ff > 0 ? l.conv2 : nullptr;
-  ca.state = l.conv_state;
-  ca.out1 = xa;
-  ca.out2 = xb;
-  ca.group = b.group;
-  ca.pos = b.pos;
-  ca.rows = rows;
-  ca.width = E;
-  ca.taps = l.conv_taps;
-  MTX_TRY(launch(input_conv_kernel<T>, dim3(rows), dim3(256), 0, st, ca));
-  if (l.conv_taps > 1)
-    MTX_TRY(launch(conv_state_update_kernel, dim3(b.n_runs, l.conv_taps - 1), dim3(256), 0, st, (const float*)e->h, l.conv_state, b.run_row0, b.group, b.pos, E,
-                   l.conv_taps));
+  if (!single_token_rows(b)) {  // (else the kernel that normed the rows has done this too)
+    MTX_TRY(launch(input_conv_kernel<T>, dim3(rows), dim3(256), 0, st, input_conv_args<T>(e, l, b)));
+    if (l.conv_taps > 1)
+      MTX_TRY(launch(conv_state_update_kernel, dim3(b.n_runs, l.conv_taps - 1), dim3(256), 0, st, (const float*)e->h, l.conv_state, b.run_row0, b.group, b.pos, E,
+                     l.conv_taps));
+  }
   MTX_TRY((linear<T, LIN_PLAIN>(e, xa, l.w_in, nullptr, e->qkv, nullptr, rows, n_in, E, st)));
   SoftmaxAttnArgs<T> sa;
   memset(&sa, 0, sizeof(sa));
@@ -1113,7 +1136,7 @@ int parallel_layer(mtx_layered* e, int li, const mtx_ragged_batch& b, cudaStream
   }
   if (l.ff > 0) MTX_TRY((linear<T, LIN_RELU2>(e, xb, l.w_gate_up, nullptr, nullptr, cat + pc.k_mix, rows, l.ff, E, st, 0.0f, k_cat)));
   MTX_TRY((linear<T, LIN_PLAIN>(e, cat, l.wo, nullptr, e->y, nullptr, rows, E, k_cat, st)));
-  return group_norm_step(e, e->y, l.residual_mult, li + 1, rows, st);
+  return group_norm_step<T>(e, e->y, l.residual_mult, li + 1, b, st);
 }
 
 template <typename T>
@@ -1124,7 +1147,7 @@ int step_typed(mtx_layered* e, const mtx_ragged_batch& b, cudaStream_t st) {
   MTX_TRY(launch(embed_rows_kernel<T>, dim3(rows), dim3(128), 0, st, b.token, static_cast<const T*>(c.embedding), c.vocab, c.embed_scale, e->x, xa, E,
                  e->sandwich ? e->x0 : (float*)nullptr));
   if (e->sandwich) MTX_TRY(sandwich_step<T>(e, nullptr, nullptr, nullptr, nullptr, 0, rows, st));  // layer 0's pre-adds and pre-norm
-  if (e->parallel) MTX_TRY(group_norm_step(e, nullptr, 0.0f, 0, rows, st));                         // layer 0's norm
+  if (e->parallel) MTX_TRY(group_norm_step<T>(e, nullptr, 0.0f, 0, b, st));                         // layer 0's norm
   for (int li = 0; li < c.num_layers; ++li) {
     if (e->layers[li].norm_style == MTX_NORM_PARALLEL) MTX_TRY(parallel_layer<T>(e, li, b, st));
     else if (e->layers[li].mixer == MTX_MIXER_COMPOSITE) MTX_TRY(composite_layer<T>(e, li, b, st));

@@ -25,10 +25,10 @@
 //                              value columns); S = Q K^T and O += P V on mma.sync m16n8k16 with fp32 accumulators, scores, running
 //                              maximum and sum in fp32 registers, K / V tiles double-buffered in shared memory by cp.async through the
 //                              page map.  For vdim == dim in {16, 32, 48, 64, 96, 128, 256}.
-//   softmax_attention_decode_kernel    bf16, steps of single tokens: one CTA per (row, key head, key split) with the products
-//                              TRANSPOSED (S^T = K Q^T, O^T = V^T P^T): the 16-row side of the MMA carries keys / value columns, the
-//                              8-column side the up to eight query heads of the key head, so no tensor-core row is spent on
-//                              padding; each of the four warps takes 16 keys of every 64-key tile and the warps' partial results
+//   softmax_attention_decode_kernel    bf16, steps of single tokens: one CTA per (row, key head, chunk of eight query heads, key
+//                              split) with the products TRANSPOSED (S^T = K Q^T, O^T = V^T P^T): the 16-row side of the MMA carries
+//                              keys / value columns, the 8-column side the chunk's query heads, so no tensor-core row is spent on
+//                              padding; when keys and values are the same rows of one pool a tile is staged once; each of the four warps takes 16 keys of every 64-key tile and the warps' partial results
 //                              are merged through shared memory.
 //   softmax_attention_merge_kernel     adds the key splits' partial results.
 #pragma once
@@ -358,6 +358,7 @@ __global__ void __launch_bounds__(128) softmax_attention_mma_kernel(const Softma
     lo += tile_lo * KT;
   }
 
+  const bool same_kv = a.k_pages == a.v_pages;  // the values are the cached keys' rows themselves: one copy of a tile serves both
   auto load_tile = [&](int it, int stage) {
     bf16* sk = stage0 + size_t(stage) * 2 * KT * PITCH;
     bf16* sv = sk + KT * PITCH;
@@ -368,7 +369,7 @@ __global__ void __launch_bounds__(128) softmax_attention_mma_kernel(const Softma
       const bool ok = j <= p_last;
       const size_t row = ok ? head_rows + size_t(pages[j / a.tokens_per_page]) * a.tokens_per_page + j % a.tokens_per_page : 0;
       cp_async_16(sk + jj * PITCH + c * 8, a.k_pages + row * D + c * 8, ok);
-      cp_async_16(sv + jj * PITCH + c * 8, a.v_pages + row * D + c * 8, ok);
+      if (!same_kv) cp_async_16(sv + jj * PITCH + c * 8, a.v_pages + row * D + c * 8, ok);
     }
     cp_async_commit();
   };
@@ -411,7 +412,7 @@ __global__ void __launch_bounds__(128) softmax_attention_mma_kernel(const Softma
     __syncthreads();
     if (active) {
       const bf16* sk = stage0 + size_t(it & 1) * 2 * KT * PITCH;
-      const bf16* sv = sk + KT * PITCH;
+      const bf16* sv = same_kv ? sk : sk + KT * PITCH;
       const int j0 = lo + it * KT;
       float s[KT / 8][4];
 #pragma unroll
@@ -530,8 +531,9 @@ __device__ __forceinline__ uint32_t smax_movmatrix_trans(uint32_t a) {
 
 constexpr int kSdecWarps = 4, kSdecKeys = 64;
 
-inline size_t softmax_decode_smem_bytes(int dim) {
-  const size_t ring = size_t(2) * kSdecKeys * 2 * (dim + 8) * sizeof(bf16), merge = sizeof(float) * kSdecWarps * (8 * size_t(dim) + 16);
+// (same_kv: keys and values are the same rows of one pool, so a tile is staged once)
+inline size_t softmax_decode_smem_bytes(int dim, bool same_kv = false) {
+  const size_t ring = size_t(2) * kSdecKeys * (same_kv ? 1 : 2) * (dim + 8) * sizeof(bf16), merge = sizeof(float) * kSdecWarps * (8 * size_t(dim) + 16);
   return ring > merge ? ring : merge;
 }
 
@@ -542,8 +544,12 @@ __global__ void __launch_bounds__(kSdecWarps * 32) softmax_attention_decode_kern
   bf16* const stage0 = reinterpret_cast<bf16*>(sdec_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   griddep_wait();
-  const int rep = a.heads / a.kv_heads;  // <= 8
-  const int row = blockIdx.x, kvh = blockIdx.y;
+  // a key head's query heads in chunks of eight (the MMA's 8-column side): blockIdx.y = (key head, chunk)
+  const int rep_all = a.heads / a.kv_heads, chunks = (rep_all + 7) / 8;
+  const int row = blockIdx.x, kvh = blockIdx.y / chunks, chunk = blockIdx.y % chunks;
+  const int rep = rep_all - chunk * 8 < 8 ? rep_all - chunk * 8 : 8, head0 = kvh * rep_all + chunk * 8;
+  const bool same_kv = a.k_pages == a.v_pages;  // the values are the cached keys' rows themselves: one copy of a tile serves both
+  const int stage_elems = (same_kv ? 1 : 2) * KT * PITCH;
   const int pos = a.pos[row], grp = a.group[row];
   int lo = 0;
   if (a.window > 0 && pos - a.window + 1 > 0) lo = pos - a.window + 1;
@@ -557,7 +563,7 @@ __global__ void __launch_bounds__(kSdecWarps * 32) softmax_attention_decode_kern
   const int first = lo + tile_lo * KT;
 
   auto load_tile = [&](int it, int stage) {
-    bf16* sk = stage0 + size_t(stage) * 2 * KT * PITCH;
+    bf16* sk = stage0 + size_t(stage) * stage_elems;
     bf16* sv = sk + KT * PITCH;
     const int j0 = first + it * KT;
     constexpr int CH = D / 8;
@@ -566,7 +572,7 @@ __global__ void __launch_bounds__(kSdecWarps * 32) softmax_attention_decode_kern
       const bool ok = j <= pos;
       const size_t r = ok ? head_rows + size_t(pages[j / a.tokens_per_page]) * a.tokens_per_page + j % a.tokens_per_page : 0;
       cp_async_16(sk + jj * PITCH + c * 8, a.k_pages + r * D + c * 8, ok);
-      cp_async_16(sv + jj * PITCH + c * 8, a.v_pages + r * D + c * 8, ok);
+      if (!same_kv) cp_async_16(sv + jj * PITCH + c * 8, a.v_pages + r * D + c * 8, ok);
     }
     cp_async_commit();
   };
@@ -574,7 +580,7 @@ __global__ void __launch_bounds__(kSdecWarps * 32) softmax_attention_decode_kern
   // the group's queries as the B operand: lane (g, t) holds head g's channels kk * 16 + 2t, + 1 and + 8 + 2t, + 9
   uint32_t qf[D16][2];
   {
-    const bf16* q = a.q + size_t(row) * a.heads * D + (kvh * rep + (g < rep ? g : 0)) * D;
+    const bf16* q = a.q + size_t(row) * a.heads * D + (head0 + (g < rep ? g : 0)) * D;
 #pragma unroll
     for (int kk = 0; kk < D16; ++kk) {
       qf[kk][0] = g < rep ? *reinterpret_cast<const uint32_t*>(q + kk * 16 + 2 * t) : 0u;
@@ -589,12 +595,12 @@ __global__ void __launch_bounds__(kSdecWarps * 32) softmax_attention_decode_kern
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};  // heads 2t, 2t + 1
   float slope0 = 0.0f, slope1 = 0.0f;
   if (a.slopes) {
-    slope0 = 2 * t < rep ? a.slopes[kvh * rep + 2 * t] : 0.0f;
-    slope1 = 2 * t + 1 < rep ? a.slopes[kvh * rep + 2 * t + 1] : 0.0f;
+    slope0 = 2 * t < rep ? a.slopes[head0 + 2 * t] : 0.0f;
+    slope1 = 2 * t + 1 < rep ? a.slopes[head0 + 2 * t + 1] : 0.0f;
   }
   if (a.sink && warp == 0 && blockIdx.z == 0) {  // (the first warp of the first split carries the sink; its eight lanes of a head are added at the end)
-    if (2 * t < rep) m_run[0] = a.sink[kvh * rep + 2 * t], l_run[0] = g == 0 ? 1.0f : 0.0f;
-    if (2 * t + 1 < rep) m_run[1] = a.sink[kvh * rep + 2 * t + 1], l_run[1] = g == 0 ? 1.0f : 0.0f;
+    if (2 * t < rep) m_run[0] = a.sink[head0 + 2 * t], l_run[0] = g == 0 ? 1.0f : 0.0f;
+    if (2 * t + 1 < rep) m_run[1] = a.sink[head0 + 2 * t + 1], l_run[1] = g == 0 ? 1.0f : 0.0f;
   }
 
   if (n_key_tiles > 0) load_tile(0, 0);
@@ -606,8 +612,8 @@ __global__ void __launch_bounds__(kSdecWarps * 32) softmax_attention_decode_kern
       cp_async_wait_pending(0);
     }
     __syncthreads();
-    const bf16* sk = stage0 + size_t(it & 1) * 2 * KT * PITCH;
-    const bf16* sv = sk + KT * PITCH;
+    const bf16* sk = stage0 + size_t(it & 1) * stage_elems;
+    const bf16* sv = same_kv ? sk : sk + KT * PITCH;
     const int j0 = first + it * KT + warp * 16;  // this warp's 16 keys
     if (j0 <= pos) {
       float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -700,7 +706,7 @@ __global__ void __launch_bounds__(kSdecWarps * 32) softmax_attention_decode_kern
         acc = fmaf(f, mo[(w * 8 + hh) * D + col], acc);
       }
     }
-    const int h = kvh * rep + hh;
+    const int h = head0 + hh;
     if (a.splits > 1) {
       const size_t base = (size_t(blockIdx.z) * a.rows + row) * a.heads + h;
       a.part_o[base * D + col] = acc;
