@@ -191,8 +191,8 @@ struct InputConvArgs {
   int rows, width, taps;
 };
 
-// one CTA of eight warps per row.  A group's sum of squares is added in a fixed order: by one warp when there are eight groups or
-// more, else by 8 / groups warps whose partial sums meet in shared memory.
+// CTAs of eight warps.  A group's sum of squares is added in a fixed order: with eight groups or more a CTA takes a row and each of
+// its warps whole groups; with fewer the grid is (rows, groups) and the eight warps' partial sums of a group meet in shared memory.
 // FUSED (steps in which every row is a single token of its own sequence): the row's normed values do not go to the plane h but
 // straight through the input convolutions (the earlier rows come from the sequence's ring) and into the ring.  The arithmetic is
 // that of input_conv_kernel, value by value, so a position's result does not depend on which of the two paths served it.
@@ -241,28 +241,25 @@ __global__ void __launch_bounds__(256) group_norm_step_kernel(const float* y, fl
     }
     return;
   }
-  const int wpg = 8 / groups, g = warp / wpg, wi = warp % wpg;
-  const bool on = g < groups;
-  const int base = g * gs;
+  const int base = int(blockIdx.y) * gs;
   float ss = 0.0f;
-  if (on) {
-    for (int c = wi * 32 + lane; c < gs; c += wpg * 32) {
-      float v = xr[base + c];
-      if (yr) {
-        v = fmaf(mult, yr[base + c], v);
-        xr[base + c] = v;
-      }
-      ss = fmaf(v, v, ss);
+  for (int c = threadIdx.x; c < gs; c += 256) {
+    float v = xr[base + c];
+    if (yr) {
+      v = fmaf(mult, yr[base + c], v);
+      xr[base + c] = v;
     }
+    ss = fmaf(v, v, ss);
   }
   ss = warp_sum(ss);
   if (lane == 0) red[warp] = ss;
   __syncthreads();
-  if (!on || !w) return;
+  if (!w) return;
   float tot = 0.0f;
-  for (int i = 0; i < wpg; ++i) tot += red[g * wpg + i];
+  for (int i = 0; i < 8; ++i) tot += red[i];
   const float f = 1.0f / sqrtf(tot / float(gs) + eps);
-  for (int c = wi * 32 + lane; c < gs; c += wpg * 32) emit(base + c, xr[base + c] * f * w[base + c]);
+#pragma unroll 2
+  for (int c = threadIdx.x; c < gs; c += 256) emit(base + c, xr[base + c] * f * w[base + c]);
 }
 
 template <typename T>
@@ -291,14 +288,39 @@ __global__ void logit_post_kernel(float* z, float scale, float cap, long long to
 
 // one CTA per row.  The row `back` steps before row r is row r - back of the batch when that is the same sequence's previous
 // position (rows of a run are consecutive), a row of the state when the run began later, and zero before the sequence's start.
+// Where each of them lies is found once per CTA (up to kConvMaxBack earlier rows; more taps take the per-element path).
+constexpr int kConvMaxBack = 16;
+
 template <typename T>
 __global__ void __launch_bounds__(256) input_conv_kernel(const InputConvArgs<T> a) {
+  __shared__ const float* s_src[kConvMaxBack];
   griddep_wait();
   const int r = blockIdx.x, W = a.width, p = a.pos[r], grp = a.group[r], ring = a.taps - 1;
+  const int n_back = ring < p ? ring : p;
+  if (ring <= kConvMaxBack) {
+    if (threadIdx.x < n_back) {
+      const int back = threadIdx.x + 1, rr = r - back;
+      const bool in_batch = rr >= 0 && a.group[rr] == grp && a.pos[rr] == p - back;
+      s_src[threadIdx.x] = in_batch ? a.h + size_t(rr) * W : a.state + (size_t(grp) * ring + (p - back) % ring) * W;
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+      const float own = a.h[size_t(r) * W + c];
+      float s1 = own * a.w1[size_t(ring) * W + c], s2 = a.w2 ? own * a.w2[size_t(ring) * W + c] : 0.0f;
+      for (int back = 1; back <= n_back; ++back) {
+        const float v = s_src[back - 1][c];
+        s1 = fmaf(v, a.w1[size_t(ring - back) * W + c], s1);
+        if (a.w2) s2 = fmaf(v, a.w2[size_t(ring - back) * W + c], s2);
+      }
+      a.out1[size_t(r) * W + c] = to_act<T>(own + s1);
+      a.out2[size_t(r) * W + c] = to_act<T>(own + s2);
+    }
+    return;
+  }
   for (int c = threadIdx.x; c < W; c += blockDim.x) {
     const float own = a.h[size_t(r) * W + c];
     float s1 = own * a.w1[size_t(ring) * W + c], s2 = a.w2 ? own * a.w2[size_t(ring) * W + c] : 0.0f;
-    for (int back = 1; back <= ring && back <= p; ++back) {
+    for (int back = 1; back <= n_back; ++back) {
       const int rr = r - back;
       const bool in_batch = rr >= 0 && a.group[rr] == grp && a.pos[rr] == p - back;
       const float v = in_batch ? a.h[size_t(rr) * W + c] : a.state[(size_t(grp) * ring + (p - back) % ring) * W + c];

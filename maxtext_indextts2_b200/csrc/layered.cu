@@ -933,12 +933,13 @@ int group_norm_step(mtx_layered* e, const float* y, float mult, int next, const 
   const float* w = last ? nullptr : e->layers[next].norm1;
   if (!y && !w) return MTX_OK;
   const mtx_layered_config& c = e->cfg;
+  const dim3 grid(b.rows, c.norm_groups < 8 ? c.norm_groups : 1);
   if (!last && single_token_rows(b))
-    return launch(group_norm_step_kernel<T, true>, dim3(b.rows), dim3(256), 0, st, y, mult, e->x, w, c.eps, e->h, c.width, c.norm_groups,
+    return launch(group_norm_step_kernel<T, true>, grid, dim3(256), 0, st, y, mult, e->x, w, c.eps, e->h, c.width, c.norm_groups,
                   input_conv_args<T>(e, e->layers[next], b));
   InputConvArgs<T> none;
   memset(&none, 0, sizeof(none));
-  return launch(group_norm_step_kernel<T, false>, dim3(b.rows), dim3(256), 0, st, y, mult, e->x, w, c.eps, e->h, c.width, c.norm_groups, none);
+  return launch(group_norm_step_kernel<T, false>, grid, dim3(256), 0, st, y, mult, e->x, w, c.eps, e->h, c.width, c.norm_groups, none);
 }
 
 // a MTX_NORM_PARALLEL layer; h holds gnorm(x, norm1) on entry

@@ -358,6 +358,7 @@ SIZES = {
     "shared_cache_two_layers_back": lambda: model([att(gi.dense_ff(24)), dlt(), att(kv_from=0, window=30), att(kv_from=0, window=2)]),
     "two_taps": lambda: model([att(gi.dense_ff(24)), dlt(gi.dense_ff(24)), lat(gi.dense_ff(24))], taps=2),
     "seven_taps": lambda: model([att(gi.dense_ff(24)), dlt(gi.dense_ff(24)), lat(gi.dense_ff(24))], taps=7),
+    "more_taps_than_the_convolution_keeps_a_table_for": lambda: model([att(gi.dense_ff(24)), dlt(gi.dense_ff(24))], taps=20),
     "layers_without_feed_forward": lambda: model([att(), dlt(), lat()]),
     "forty_norm_groups": lambda: model([att(gi.dense_ff(24)), dlt()], groups=40),
     "eight_norm_groups": lambda: model([att(gi.dense_ff(24)), dlt()], groups=8),
