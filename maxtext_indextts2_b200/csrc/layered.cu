@@ -607,13 +607,28 @@ int launch_softmax_decode_t(const SoftmaxAttnArgs<bf16>& sa, cudaStream_t st) {
   return launch(softmax_attention_decode_kernel<D16>, dim3(sa.rows, sa.kv_heads * chunks, sa.splits), dim3(kSdecWarps * 32), smem, st, sa);
 }
 
-// a step of single tokens (every row its own tile and sequence): the transposed kernel, its keys cut into splits until every SM
-// has about three CTAs (what its shared memory lets an SM hold)
+// a step of single tokens (every row its own tile and sequence): the transposed kernel.  Its keys are cut into one to four splits,
+// the count that makes the waves of CTAs (as many CTAs at once as the kernel's shared memory lets the GPU hold) times a split's
+// length shortest; a split's start-up counts like two key tiles, and a sequence without a window like one of 2048 keys
 int launch_softmax_decode(mtx_layered* e, SoftmaxAttnArgs<bf16> sa, int d16, cudaStream_t st) {
   const long long ctas = (long long)sa.rows * sa.kv_heads * ((sa.heads / sa.kv_heads + 7) / 8);
-  long long sp = (3LL * e->num_sms + ctas - 1) / ctas;
-  sa.splits = int(sp > 4 ? 4 : (sp < 1 ? 1 : sp));
-  if (size_t(sa.splits) * sa.rows > e->attn_part_rows) sa.splits = 1;
+  const size_t smem = softmax_decode_smem_bytes(sa.dim, sa.k_pages == sa.v_pages);
+  long long per_sm = (long long)((227 * 1024) / (smem + 1024));
+  per_sm = per_sm > 16 ? 16 : (per_sm < 1 ? 1 : per_sm);
+  const long long slots = per_sm * e->num_sms;
+  const double tiles = sa.window > 0 ? double((sa.window + kSdecKeys - 1) / kSdecKeys) : 32.0;
+  static const int force = env_int("MTX_SOFTMAX_DECODE_SPLITS", 0);
+  double best = 0.0;
+  sa.splits = 1;
+  for (int sp = 1; sp <= 4; ++sp) {
+    if (size_t(sp) * sa.rows > e->attn_part_rows) break;
+    const double cost = double((ctas * sp + slots - 1) / slots) * (tiles / sp + 2.0);
+    if (sp == 1 || cost < best - 1e-9) {
+      best = cost;
+      sa.splits = sp;
+    }
+  }
+  if (force >= 1 && force <= 4 && size_t(force) * sa.rows <= e->attn_part_rows) sa.splits = force;
   sa.part_o = e->attn_part;
   sa.part_ml = e->smax_ml;
   int rc = MTX_ERR_UNSUPPORTED;
@@ -1098,7 +1113,7 @@ int parallel_layer(mtx_layered* e, int li, const mtx_ragged_batch& b, cudaStream
     pa.w_bias = r.decay_bias;
     pa.a_bias = r.gate_bias;
     pa.out = e->rec_aux;
-    MTX_TRY(launch(delta_prepare_kernel, dim3(rows), dim3(256), sizeof(float) * r.decay_rank, st, pa));
+    MTX_TRY(launch(delta_prepare_kernel, dim3(rows, (r.heads + 7) / 8), dim3(256), sizeof(float) * r.decay_rank, st, pa));
     RecScanArgs ra;
     memset(&ra, 0, sizeof(ra));
     ra.proj = e->qkv;

@@ -78,7 +78,7 @@ struct DeltaPrepareArgs {
   float* out;          // [rows, 3, heads * dim]: decays w, unit keys u, removal vectors a * u
 };
 
-// one CTA per row, a warp per head
+// grid (rows, ceil(heads / 8)): a warp per head
 __global__ void __launch_bounds__(256) delta_prepare_kernel(const DeltaPrepareArgs a) {
   extern __shared__ float s_low[];
   griddep_wait();
@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(256) delta_prepare_kernel(const DeltaPrepareAr
   for (int e = threadIdx.x; e < a.rank; e += blockDim.x) s_low[e] = tanhf(row[a.x_col + e]);
   __syncthreads();
   float* out = a.out + size_t(r) * 3 * n;
-  for (int h = warp; h < a.heads; h += 8) {
+  for (int h = blockIdx.y * 8 + warp; h < a.heads; h += 8 * gridDim.y) {
     const float* k = row + a.k_col + h * d;
     float ss = 0.0f;
     for (int c = lane; c < d; c += 32) ss = fmaf(k[c], k[c], ss);
@@ -96,6 +96,7 @@ __global__ void __launch_bounds__(256) delta_prepare_kernel(const DeltaPrepareAr
     for (int c = lane; c < d; c += 32) {
       const int col = h * d + c;
       float z = a.w_bias ? a.w_bias[col] : 0.0f;
+#pragma unroll 8
       for (int e = 0; e < a.rank; ++e) z = fmaf(a.up_t[size_t(e) * n + col], s_low[e], z);
       const float u = k[c] * inv;
       const float rem = 1.0f / (1.0f + expf(-(row[a.a_col + col] + (a.a_bias ? a.a_bias[col] : 0.0f))));
