@@ -1275,6 +1275,7 @@ int check_parallel(mtx_layered* e, int i) {
     if (softmax_attn_smem_bytes(dl, dl) > 200 * 1024) return fail(MTX_ERR_UNSUPPORTED, "layer %d: the latent rows do not fit shared memory", i);
     if (m.heads * dl > e->max_qdim) e->max_qdim = m.heads * dl;
     if (m.heads * dl > e->max_lat_o) e->max_lat_o = m.heads * dl;
+    if (m.heads * dl > e->max_odim) e->max_odim = m.heads * dl;  // (the key splits' partial results are sized by max_odim)
     if (m.heads * m.dim > e->max_lat_o) e->max_lat_o = m.heads * m.dim;
     if (m.heads * (m.dim + m.rot_dim) > e->max_lat_q) e->max_lat_q = m.heads * (m.dim + m.rot_dim);
     if (m.q_rank > e->max_ff) e->max_ff = m.q_rank;  // (the query latent waits in the plane of the feed-forward's activation)

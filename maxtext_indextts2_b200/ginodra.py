@@ -58,7 +58,7 @@ def config_keys(model: dict) -> dict:
       normalization_layer_epsilon=float(model["norm"]["eps"]),
       norm_groups=int(model["norm"].get("groups", 1)),
       residual_multiplier=float(model.get("residual_mult", 1.0)),
-      input_conv_taps=int(model["canon"]["taps"]) if model.get("canon") else 1,
+      input_conv_taps=int(model["canon"]["taps"]) if model.get("canon") else 0,  # (0: the model has no input convolutions)
       logits_scale=float(model.get("logit_scale", 1.0)),
       final_logits_soft_cap=float(model.get("logit_softcap") or 0.0),
       layer_specs=layers,
@@ -102,7 +102,10 @@ def validate_layer_specs(specs: List[dict]) -> None:
 
 
 def _conv_taps_major(t: Dict[str, torch.Tensor], name: str, E: int, taps: int) -> torch.Tensor:
-  """[width, taps] as stored -> [taps, width] fp32 (the kernels read a tap's weights of neighbouring channels together)."""
+  """[width, taps] as stored -> [taps, width] fp32 (the kernels read a tap's weights of neighbouring channels together).  A model
+  without input convolutions (taps == 0) gets one tap of zeros: h + 0 * h."""
+  if taps == 0:
+    return torch.zeros(1, E, dtype=torch.float32, device=t["embed"].device)
   return _shape(t[name].to(torch.float32), (E, taps), name).t().contiguous()
 
 
@@ -117,7 +120,7 @@ def layer_plan(config, tensors: Dict[str, torch.Tensor], i: int) -> Dict[str, An
   f32 = lambda name: t[name].to(torch.float32)
   m = spec["mixer"]
   plan: Dict[str, Any] = dict(mixer="composite", norm_style="parallel", attn=None, rec=None, latent=None, moe=None, ff_kind="relu2", ff=0,
-                              residual_mult=float(config.residual_multiplier), conv_taps=taps,
+                              residual_mult=float(config.residual_multiplier), conv_taps=max(taps, 1),
                               norm1=_shape(f32(f"l{i}.norm1"), (E,), f"l{i}.norm1"), conv1=_conv_taps_major(t, f"l{i}.canon1", E, taps), conv2=None)
   rows: List[torch.Tensor] = []
   if spec["type"] == "attention":
@@ -199,7 +202,8 @@ def random_tensors(config, seed: int = 0, device: Any = "cpu") -> Dict[str, torc
   for i, l in enumerate(config.layer_specs):
     p, m = f"l{i}.", l["mixer"]
     t[p + "norm1"] = rn(E, std=0.1, mean=1.0)
-    t[p + "canon1"] = rn(E, taps, std=0.3)
+    if taps:
+      t[p + "canon1"] = rn(E, taps, std=0.3)
     q = p + "mix."
     if l["type"] == "attention":
       H, G, d, dv = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
@@ -222,7 +226,9 @@ def random_tensors(config, seed: int = 0, device: Any = "cpu") -> Dict[str, torc
     f = l.get("mlp")
     if f:
       F = int(f["ff"])
-      t[p + "canon2"], t[p + "mlp.up"], t[p + "mlp.down"] = rn(E, taps, std=0.3), lin(F, E), lin(E, F)
+      t[p + "mlp.up"], t[p + "mlp.down"] = lin(F, E), lin(E, F)
+      if taps:
+        t[p + "canon2"] = rn(E, taps, std=0.3)
   return t
 
 

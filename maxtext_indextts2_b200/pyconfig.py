@@ -134,8 +134,8 @@ def _validate_layered(keys: dict) -> None:
     ginodra.validate_layer_specs(keys["layer_specs"])
     if int(keys["norm_groups"]) < 1 or int(keys["emb_dim"]) % int(keys["norm_groups"]):
       raise ValueError("norm_groups must divide the width")
-    if int(keys["input_conv_taps"]) < 1:
-      raise ValueError("input_conv_taps must be positive")
+    if int(keys["input_conv_taps"]) < 0:
+      raise ValueError("input_conv_taps must not be negative")
 
 
 def _validate(keys: dict) -> None:

@@ -177,7 +177,8 @@ def forward(model: dict, tensors: Dict[str, np.ndarray], tokens: List[int], retu
   for i, layer in enumerate(model["layers"]):
     pre = f"l{i}."
     h = group_norm(x, tensors[pre + "norm1"], groups, eps)
-    hm = h + causal_conv(h, tensors[pre + "canon1"])
+    conv = (lambda z, name: z + causal_conv(z, tensors[name])) if model.get("canon") else (lambda z, name: z)
+    hm = conv(h, pre + "canon1")
     spec, p = layer["mixer"], sub(tensors, pre + "mix.")
     if layer["type"] == "attention":
       src = spec.get("kv_from")
@@ -189,7 +190,7 @@ def forward(model: dict, tensors: Dict[str, np.ndarray], tokens: List[int], retu
     else:
       raise ValueError(layer["type"])
     if layer.get("mlp"):
-      hf = h + causal_conv(h, tensors[pre + "canon2"])
+      hf = conv(h, pre + "canon2")
       y = y + squared_relu_ff(hf, tensors[pre + "mlp.up"], tensors[pre + "mlp.down"])
     x = x + m * y
     stream.append(x.copy())
@@ -212,14 +213,16 @@ def random_model(model: dict, seed: int = 0, rank: int = 6) -> Dict[str, np.ndar
   """Random weights by the stored names, already rounded to bfloat16 values.  `rank`: the decay's low rank of general_delta layers."""
   g = np.random.Generator(np.random.PCG64(seed))
   E, V = int(model["width"]), int(model["vocab"])
-  taps = int(model["canon"]["taps"])
+  taps = int(model["canon"]["taps"]) if model.get("canon") else 0
   t: Dict[str, np.ndarray] = {}
   rn = lambda *shape, std=1.0, mean=0.0: bf16_values(g.normal(mean, std, size=shape))
   lin = lambda n, k: rn(n, k, std=1.0 / math.sqrt(k))
   t["embed"], t["final.norm"] = rn(V, E), rn(E, std=0.2, mean=1.0)
   for i, layer in enumerate(model["layers"]):
     p, q, m = f"l{i}.", f"l{i}.mix.", layer["mixer"]
-    t[p + "norm1"], t[p + "canon1"] = rn(E, std=0.2, mean=1.0), rn(E, taps, std=0.4)
+    t[p + "norm1"] = rn(E, std=0.2, mean=1.0)
+    if taps:
+      t[p + "canon1"] = rn(E, taps, std=0.4)
     if layer["type"] == "attention":
       H, G, d, dv = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
       t[q + "q"], t[q + "q.norm"], t[q + "g"], t[q + "o"] = lin(H * d, E), rn(d, std=0.3, mean=1.5), lin(H, E), lin(E, H * dv)
@@ -239,5 +242,7 @@ def random_model(model: dict, seed: int = 0, rank: int = 6) -> Dict[str, np.ndar
       t[q + "norm"], t[q + "o"] = rn(H * d, std=0.2, mean=1.0), lin(E, H * d)
     if layer.get("mlp"):
       F = int(layer["mlp"]["ff"])
-      t[p + "canon2"], t[p + "mlp.up"], t[p + "mlp.down"] = rn(E, taps, std=0.4), lin(F, E), lin(E, F)
+      t[p + "mlp.up"], t[p + "mlp.down"] = lin(F, E), lin(E, F)
+      if taps:
+        t[p + "canon2"] = rn(E, taps, std=0.4)
   return t

@@ -89,6 +89,7 @@ CASES = {
     "delta_rule_one_head": lambda: model([dlt(heads=1, dim=20)]),
     "feed_forward": lambda: model([dlt(gi.dense_ff(56))]),
     "no_conv_taps": lambda: model([att(gi.dense_ff(24))], taps=1),
+    "no_input_convolutions_at_all": lambda: {k: v for k, v in model([att(gi.dense_ff(24)), dlt()]).items() if k != "canon"},
     "five_taps": lambda: model([att(gi.dense_ff(24)), dlt(gi.dense_ff(24))], taps=5),
     "one_norm_group": lambda: model([att(gi.dense_ff(24))], groups=1),
     "ten_norm_groups": lambda: model([lat(gi.dense_ff(24))], groups=10),
@@ -360,7 +361,7 @@ SIZES = {
     "seven_taps": lambda: model([att(gi.dense_ff(24)), dlt(gi.dense_ff(24)), lat(gi.dense_ff(24))], taps=7),
     "more_taps_than_the_convolution_keeps_a_table_for": lambda: model([att(gi.dense_ff(24)), dlt(gi.dense_ff(24))], taps=20),
     "layers_without_feed_forward": lambda: model([att(), dlt(), lat()]),
-    "forty_norm_groups": lambda: model([att(gi.dense_ff(24)), dlt()], groups=40),
+    "ten_norm_groups": lambda: model([att(gi.dense_ff(24)), dlt()], groups=10),  # (groups of one or two channels make x / sqrt(x^2 + eps) ill-conditioned near 0)
     "eight_norm_groups": lambda: model([att(gi.dense_ff(24)), dlt()], groups=8),
     "five_norm_groups": lambda: model([att(gi.dense_ff(24)), dlt()], groups=5),
 }
@@ -398,13 +399,15 @@ def test_bfloat16_engine_is_within_rounding_of_the_exact_model(case):
 # ---- the tensor-core attention with the optional parts (bf16, head sizes in multiples of 16) ----------------------------------------
 
 @pytest.mark.parametrize("kind,heads,kv_heads,dim,page", [("att", 4, 2, 64, 16), ("att", 2, 2, 16, 8), ("att", 8, 1, 32, 64), ("att", 6, 2, 48, 4),
-                                                          ("lat", 8, 1, 64, 16), ("lat", 3, 1, 128, 32), ("lat", 16, 1, 96, 16), ("lat", 2, 1, 256, 16)])
+                                                          ("lat", 8, 1, 64, 16), ("lat", 3, 1, 128, 32), ("lat_narrow_ff", 12, 1, 128, 16), ("lat", 16, 1, 96, 16), ("lat", 2, 1, 256, 16)])
 def test_tensor_core_attention_shapes_and_schedules(kind, heads, kv_heads, dim, page):
   """Head sizes of the tensor-core arm with slopes and a window (attention) or a sink and one key head (latent attention, `dim`
   = latent + rotated part), prompts in portions that end inside, at and after the 64-key tiles, 16-row query tiles that start
   anywhere, then single tokens; peaky scores so that single far keys matter."""
   if kind == "att":
     layers = [att(heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, window=70), att(gi.dense_ff(32), heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, window=0)]
+  elif kind == "lat_narrow_ff":  # (the key splits' partial results are wider than any activation of the model)
+    layers = [lat(gi.dense_ff(16), heads=heads, dim=8, rot_dim=dim // 4, vdim=8, q_rank=24, kv_rank=dim - dim // 4)]
   else:
     layers = [lat(heads=heads, dim=16, rot_dim=dim // 4, vdim=24, q_rank=24, kv_rank=dim - dim // 4), dlt(gi.dense_ff(32), heads=2, dim=16)]
   cfg = model(layers, width=64, vocab=90, softcap=0.0)

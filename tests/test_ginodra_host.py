@@ -79,7 +79,7 @@ def test_input_projection_is_padded_to_whole_tiles_when_the_width_allows():
     (lambda c: c["layers"][3]["mixer"].pop("kv_rank"), "kv_rank"),
     (lambda c: c["layers"][1]["mlp"].update(kind="moe"), "feed-forward kind"),
     (lambda c: c["norm"].update(groups=3), "norm_groups"),
-    (lambda c: c["canon"].update(taps=0), "input_conv_taps"),
+    (lambda c: c["canon"].update(taps=-1), "input_conv_taps"),
     (lambda c: c.update(architecture="Other"), "architecture"),
 ])
 def test_bad_configs_are_refused(break_it, match):
