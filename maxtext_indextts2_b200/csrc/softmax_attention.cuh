@@ -348,6 +348,7 @@ __global__ void __launch_bounds__(128) softmax_attention_mma_kernel(const Softma
   if (a.window > 0 && p0 - a.window + 1 > 0) lo = p0 - a.window + 1;
   const int* pages = a.page_map + size_t(grp) * a.max_pages;
   const size_t head_rows = size_t(kvh) * a.num_pages * a.tokens_per_page;
+  const int page_shift = (a.tokens_per_page & (a.tokens_per_page - 1)) == 0 ? __ffs(a.tokens_per_page) - 1 : -1;  // pages of 2^n tokens: no division per key
   const int all_key_tiles = (p_last - lo) / KT + 1;
   int tile_lo = 0, n_key_tiles = all_key_tiles;
   if (a.splits > 1) {
@@ -367,7 +368,8 @@ __global__ void __launch_bounds__(128) softmax_attention_mma_kernel(const Softma
     for (int e = tid; e < KT * CH; e += nthreads) {
       const int jj = e / CH, c = e % CH, j = j0 + jj;
       const bool ok = j <= p_last;
-      const size_t row = ok ? head_rows + size_t(pages[j / a.tokens_per_page]) * a.tokens_per_page + j % a.tokens_per_page : 0;
+      const int pg = page_shift >= 0 ? (j >> page_shift) : j / a.tokens_per_page;
+      const size_t row = ok ? head_rows + size_t(pages[pg]) * a.tokens_per_page + (j - pg * a.tokens_per_page) : 0;
       cp_async_16(sk + jj * PITCH + c * 8, a.k_pages + row * D + c * 8, ok);
       if (!same_kv) cp_async_16(sv + jj * PITCH + c * 8, a.v_pages + row * D + c * 8, ok);
     }
@@ -555,6 +557,7 @@ __global__ void __launch_bounds__(kSdecWarps * 32) softmax_attention_decode_kern
   if (a.window > 0 && pos - a.window + 1 > 0) lo = pos - a.window + 1;
   const int* pages = a.page_map + size_t(grp) * a.max_pages;
   const size_t head_rows = size_t(kvh) * a.num_pages * a.tokens_per_page;
+  const int page_shift = (a.tokens_per_page & (a.tokens_per_page - 1)) == 0 ? __ffs(a.tokens_per_page) - 1 : -1;  // pages of 2^n tokens: no division per key
   const int all_key_tiles = (pos - lo) / KT + 1;
   const int per = (all_key_tiles + a.splits - 1) / a.splits;
   const int tile_lo = int(blockIdx.z) * per;
@@ -570,7 +573,8 @@ __global__ void __launch_bounds__(kSdecWarps * 32) softmax_attention_decode_kern
     for (int e = tid; e < KT * CH; e += NT) {
       const int jj = e / CH, c = e % CH, j = j0 + jj;
       const bool ok = j <= pos;
-      const size_t r = ok ? head_rows + size_t(pages[j / a.tokens_per_page]) * a.tokens_per_page + j % a.tokens_per_page : 0;
+      const int pg = page_shift >= 0 ? (j >> page_shift) : j / a.tokens_per_page;
+      const size_t r = ok ? head_rows + size_t(pages[pg]) * a.tokens_per_page + (j - pg * a.tokens_per_page) : 0;
       cp_async_16(sk + jj * PITCH + c * 8, a.k_pages + r * D + c * 8, ok);
       if (!same_kv) cp_async_16(sv + jj * PITCH + c * 8, a.v_pages + r * D + c * 8, ok);
     }
