@@ -379,6 +379,19 @@ def test_other_sizes(case):
   assert rel_err(np.concatenate(got), want) < TIGHT
 
 
+@pytest.mark.parametrize("case", sorted(SIZES))
+def test_other_sizes_on_a_bfloat16_engine(case):
+  # (odd widths and sizes take the unvectorised loads of the tensor-core projections and the row kernel of the attention)
+  cfg = SIZES[case]()
+  t = ref.random_model(cfg, seed=14)
+  toks = tokens_for(cfg, 41)
+  want = ref.forward(cfg, t, toks)
+  engine = make_engine(cfg, t, dtype="bfloat16", tokens_per_page=8)
+  got = [engine.step([(0, toks[:22], list(range(22)))]).cpu().numpy(), engine.step([(0, toks[22:39], list(range(17)))]).cpu().numpy()]
+  got += [engine.step([(0, [tok], [0])]).cpu().numpy() for tok in toks[39:]]
+  assert rms_err(np.concatenate(got), want) < 3e-2
+
+
 @pytest.mark.parametrize("case", ["default", "tiles"])
 def test_bfloat16_engine_is_within_rounding_of_the_exact_model(case):
   if case == "default":
@@ -453,7 +466,47 @@ def test_greedy_generation_through_the_offline_engine():
     assert out.token_ids.tolist() == seq[len(prompt):]
 
 
-# ---- the command line: a trace of batched steps replayed through bin/trace_run --------------------------------------------------------
+# ---- the command lines: prompts in, tokens out; a trace of batched steps replayed through bin/trace_run --------------------------------
+
+def _write_model_dir(path, cfg, t):
+  import json
+  import os
+
+  from tests.test_gugidra_host import _write_safetensors
+
+  os.makedirs(path)
+  with open(path / "config.json", "w") as f:
+    json.dump(cfg, f)
+  _write_safetensors(path / "model.safetensors", as_torch(t))
+
+
+def test_decode_command_line_generates_the_oracles_greedy_tokens(tmp_path):
+  import json
+  import os
+  import subprocess
+  import sys
+
+  cfg = DEFAULT()
+  t = ref.random_model(cfg, seed=19)
+  _write_model_dir(tmp_path / "model", cfg, t)
+  prompts = [tokens_for(cfg, n, seed=50 + n) for n in (7, 3)]
+  root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+  cmd = [sys.executable, "-m", "maxtext_indextts2_b200.decode", f"model_dir={tmp_path / 'model'}", "dtype=float32", "decode_sampling_strategy=greedy",
+         "pagedattn_tokens_per_page=8", "--max-decode", "6"]
+  for p in prompts:
+    cmd += ["--prompt", ",".join(str(x) for x in p)]
+  r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=root)
+  assert r.returncode == 0, r.stderr[-2000:]
+  outs = {d["prompt"]: d["tokens"] for d in (json.loads(l) for l in r.stdout.splitlines() if l.startswith("{"))}
+  for i, prompt in enumerate(prompts):
+    seq = list(prompt)
+    for _ in range(6):
+      logits = ref.forward(cfg, t, seq)[-1]
+      top2 = np.sort(logits)[-2:]
+      assert float(top2[1] - top2[0]) > 1e-4, "near-tie in the test's own model; change the seed"
+      seq.append(int(logits.argmax()))
+    assert outs[i] == seq[len(prompt):]
+
 
 @pytest.mark.parametrize("dtype,tol", [("float32", TIGHT), ("bfloat16", 5e-2)])  # (bfloat16: per step, some of few rows)
 def test_trace_runner_replays_a_mixed_schedule(tmp_path, dtype, tol):
@@ -461,15 +514,10 @@ def test_trace_runner_replays_a_mixed_schedule(tmp_path, dtype, tol):
   import os
   import subprocess
 
-  from tests.test_gugidra_host import _write_safetensors
-
   cfg = DEFAULT()
   t = ref.random_model(cfg, seed=23)
   model_dir = tmp_path / "model"
-  os.makedirs(model_dir)
-  with open(model_dir / "config.json", "w") as f:
-    json.dump(cfg, f)
-  _write_safetensors(model_dir / "model.safetensors", as_torch(t))
+  _write_model_dir(model_dir, cfg, t)
   lens = {"a": 70, "b": 9, "c": 33, "d": 5, "e": 40, "f": 20}
   toks = {k: tokens_for(cfg, n, seed=ord(k)) for k, n in lens.items()}
   # four pages of 64 tokens: a, b, c fill them (2 + 1 + 1); d, e and f fit only into what b and c give back, and take their slots
