@@ -373,6 +373,12 @@ int mtx_engine_rebind_state(mtx_engine* e, const mtx_decode_state* s);
                                convolution over time on each channel (conv_taps taps, zeros before the sequence's start; the last
                                conv_taps - 1 rows of h are state of the sequence).  Mixer and feed-forward share ONE output projection
                                over their concatenated activations */
+#define MTX_NORM_PRE 3      /* pre-norms whose weight is used as stored, sublayers one after the other:
+                               h = unit(x) * norm1;  x += mixer(h + conv1(h))  (conv1 as above; with two taps (s, -s) this is the
+                               token shift h + (h_prev - h) s);  x += ff(unit(x) * norm2) if the layer has a feed-forward;  then, with
+                               a side input, x += unit(side_proj(gelu_tanh(side_gate x) * side_embed[token, side_col ..])) * side_norm.
+                               The embedding output is normed with mtx_layered_config.embed_norm, the final norm uses its weight as
+                               stored.  One mixer per layer: attn or rec (MTX_REC_GDELTA) */
 
 #define MTX_FF_GELU_GATED 0    /* down(gelu_tanh(gate x) * up x) */
 #define MTX_FF_CLAMPED_GATED 1 /* down(g s(1.702 g) (u + 1)), g = min(gate x, limit), u = clamp(up x, -limit, limit), s = sigmoid */
@@ -403,6 +409,18 @@ typedef struct {
   const float* k_norm;     /* [dim] or NULL: the same for the key heads, before they are cached */
   const float* slopes;     /* [heads] or NULL: slopes[h] * (i - j) is taken off the scaled score of key j for the query at i */
   const float* sink;       /* [heads] or NULL: exp(sink[h]) is added to the softmax's denominator (no key, no value, not scaled) */
+  float softcap;           /* > 0: the scaled score becomes softcap * tanh(score / softcap) */
+  int32_t norm_whole;      /* 1: q_norm is [heads*dim] and k_norm [kv_heads*dim]: the whole projection is brought to unit RMS at once
+                              (not head by head), then multiplied by the weight, channel by channel */
+  int32_t pool;            /* P > 0 (needs a window): beside the window's tokens a query at i sees ONE key / value per block of P
+                              tokens that lies wholly before the window (block b = positions bP .. bP + P - 1, seen when
+                              bP + P - 1 <= i - window): the mean of the block's keys as cached and the mean of its values, in the
+                              same softmax.  Tokens that left the window and whose block is not complete before it are not seen */
+  int32_t pool_slots;      /* blocks per page of the pooled pools: tokens_per_page / P when P divides it, else tokens_per_page;
+                              block b lives in page page_map[b / pool_slots], slot b % pool_slots */
+  int32_t pool_shared;     /* 1: the pooled pools belong to the layer whose cache this one reads (same P), which fills them */
+  void* kp_pages;          /* [kv_heads, num_pages, pool_slots, dim] */
+  void* vp_pages;          /* [kv_heads, num_pages, pool_slots, vdim] */
 } mtx_softmax_attn_desc;
 
 /* Attention through latents (csrc/latent_attention.cuh): queries q = w_uq rmsnorm(dq x) laid out per head as [dim plain | rot_dim
@@ -433,6 +451,14 @@ typedef struct {
                            u = k / sqrt(|k|^2 + key_eps) per head; w = exp(-decay_rate sigmoid(z)) per key channel with
                            z = up tanh(down x) + decay_bias; a = sigmoid(a x + gate_bias) per key channel.  Projection rows:
                            [q | k | v | output gate: heads*vdim | a: heads*dim | decay_rank rows of the decay's down-projection] */
+#define MTX_REC_GDELTA 4 /* gated delta rule: S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q (the read-out sees the
+                           token's own write).  q, k (kv_heads heads; head h reads q / k head h / (heads / kv_heads)) and v first pass
+                           a causal convolution over time per channel (conv_taps taps, weights conv_w, the last conv_taps - 1
+                           projection rows are state) and silu; q and k are then unit vectors x / sqrt(|x|^2 + key_eps), q times
+                           q_scale.  beta = sigmoid(.).  g = exp(-exp(a_log[h]) softplus(z + decay_bias)): decay_rank == 0: one z per
+                           head from a projection row; else per key channel, z = up (down x).  Output gate: gate_rank == 0: heads*vdim
+                           projection rows; else w_gate_up (gate_rank rows of the projection).  Projection rows: [q: kv_heads*dim |
+                           k: kv_heads*dim | v: heads*vdim | beta: heads | decay: heads or decay_rank | gate: heads*vdim or gate_rank] */
 
 /* A linear recurrence with a matrix state per head (csrc/recurrent_mixers.cuh).  State, decays and gates are fp32.  Its
  * projection rows in w_in follow the attention's: [q: heads*dim | k: heads*dim | v: heads*vdim | output gate: heads*vdim |
@@ -455,10 +481,18 @@ typedef struct {
   float* state_n;          /* mLSTM: [state slots, heads, dim] */
   float* state_m;          /* mLSTM: [state slots, heads] */
   float decay_rate;        /* MTX_REC_DELTA */
-  float key_eps;           /* MTX_REC_DELTA */
+  float key_eps;           /* MTX_REC_DELTA, MTX_REC_GDELTA */
+  /* -- MTX_REC_GDELTA -- */
+  int32_t kv_heads;        /* heads of q and k; 0: as many as `heads` */
+  int32_t conv_taps;
+  int32_t gate_rank;
+  const float* conv_w;     /* [conv_taps, 2*kv_heads*dim + heads*vdim]: tap j multiplies the row conv_taps - 1 - j steps back */
+  float* conv_state;       /* [state slots, conv_taps - 1, 2*kv_heads*dim + heads*vdim]: the projection row of position p at p % (conv_taps - 1) */
+  const float* a_log;      /* [heads] */
+  const void* w_gate_up;   /* [heads*vdim, gate_rank] in the matmul dtype, or NULL */
 } mtx_recurrent_desc;
 
-/* Routed feed-forward (csrc/moe.cuh): scores s = sigmoid(router x); an expert is chosen by s + correction among the experts of
+/* Routed feed-forward (csrc/moe.cuh): scores s = sigmoid(router x) (score_softmax: softmax over all experts); an expert is chosen by s + correction among the experts of
  * the keep_groups best groups (a group = experts / groups neighbours, scored by the sum of its two largest choice scores), the
  * `top` largest; the chosen experts' outputs are weighted by s / (sum of the chosen s + 1e-20).  shared_ff > 0 adds an expert
  * that every row uses. */
@@ -473,6 +507,9 @@ typedef struct {
   const void* w_down;      /* [experts, width, ff] */
   const void* shared_gate_up; /* [2*shared_ff, width] */
   const void* shared_down;    /* [width, shared_ff] */
+  int32_t score_softmax;   /* 1: s = softmax(router x) over all experts instead of the sigmoid */
+  int32_t plain_weights;   /* 1: the chosen experts' scores are the weights as they are (no renormalisation) */
+  int32_t act_silu;        /* 1: an expert is down(silu(gate x) * up x) (no limits) instead of the clamped form */
 } mtx_moe_desc;
 
 typedef struct {
@@ -524,6 +561,12 @@ typedef struct {
   const float* conv1;      /* [conv_taps, width] (tap-major: tap j multiplies the row conv_taps - 1 - j steps back), mixer input */
   const float* conv2;      /* the same for the feed-forward's input, or NULL */
   float* conv_state;       /* [state slots, conv_taps - 1, width]: the normed row of position p is kept at index p % (conv_taps - 1) */
+  /* -- MTX_NORM_PRE layers: the side input (side_dim == 0: none) -- */
+  int32_t side_dim;
+  int32_t side_col;        /* first of the layer's side_dim columns of mtx_layered_config.side_embed */
+  const void* side_gate;   /* [side_dim, width] */
+  const void* side_proj;   /* [width, side_dim] */
+  const float* side_norm;  /* [width] */
 } mtx_layer_desc;
 
 typedef struct {
@@ -548,6 +591,10 @@ typedef struct {
   int32_t norm_groups;         /* MTX_NORM_PARALLEL models: parts of a row that are normed on their own (also in the final norm, whose
                                   weight is then used as stored); 0 for the other norm styles */
   float logit_scale;           /* multiplies the logits before the cap; 0 = 1 */
+  /* -- MTX_NORM_PRE models -- */
+  const float* embed_norm;     /* [width] or NULL: the embedding output becomes unit(.) * embed_norm */
+  const void* side_embed;      /* [vocab, side_width] rows of the per-layer token inputs, or NULL */
+  int32_t side_width;
 } mtx_layered_config;
 
 typedef struct {

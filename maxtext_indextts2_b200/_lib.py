@@ -109,9 +109,9 @@ class DecodeState(ctypes.Structure):
 
 
 MIXER_WINDOW_SIGMOID, MIXER_COMPOSITE = 1, 2
-NORM_OUT_GAIN, NORM_SANDWICH, NORM_PARALLEL = 0, 1, 2
+NORM_OUT_GAIN, NORM_SANDWICH, NORM_PARALLEL, NORM_PRE = 0, 1, 2, 3
 FF_GELU_GATED, FF_CLAMPED_GATED, FF_MOE, FF_RELU2 = 0, 1, 2, 3
-REC_GLA, REC_MLSTM, REC_DELTA = 1, 2, 3
+REC_GLA, REC_MLSTM, REC_DELTA, REC_GDELTA = 1, 2, 3, 4
 
 
 class SoftmaxAttnDesc(ctypes.Structure):
@@ -123,6 +123,9 @@ class SoftmaxAttnDesc(ctypes.Structure):
       + [(n, ctypes.c_void_p) for n in ("rot_freq", "k_pages", "v_pages")]
       + [(n, ctypes.c_int32) for n in ("rot_half", "shared_kv", "head_gate")]
       + [(n, ctypes.c_void_p) for n in ("q_norm", "k_norm", "slopes", "sink")]
+      + [("softcap", ctypes.c_float)]
+      + [(n, ctypes.c_int32) for n in ("norm_whole", "pool", "pool_slots", "pool_shared")]
+      + [(n, ctypes.c_void_p) for n in ("kp_pages", "vp_pages")]
   )
 
 
@@ -144,6 +147,8 @@ class RecurrentDesc(ctypes.Structure):
       + [(n, ctypes.c_float) for n in ("q_scale", "tau", "gate_cap", "denom_eps", "out_scale")]
       + [(n, ctypes.c_void_p) for n in ("decay_up_t", "decay_bias", "gate_bias", "out_norm", "state_s", "state_n", "state_m")]
       + [(n, ctypes.c_float) for n in ("decay_rate", "key_eps")]
+      + [(n, ctypes.c_int32) for n in ("kv_heads", "conv_taps", "gate_rank")]
+      + [(n, ctypes.c_void_p) for n in ("conv_w", "conv_state", "a_log", "w_gate_up")]
   )
 
 
@@ -154,6 +159,7 @@ class MoeDesc(ctypes.Structure):
       [(n, ctypes.c_int32) for n in ("experts", "top", "groups", "keep_groups", "ff", "shared_ff")]
       + [(n, ctypes.c_float) for n in ("limit", "shared_limit")]
       + [(n, ctypes.c_void_p) for n in ("w_router", "correction", "w_gate_up", "w_down", "shared_gate_up", "shared_down")]
+      + [(n, ctypes.c_int32) for n in ("score_softmax", "plain_weights", "act_silu")]
   )
 
 
@@ -171,6 +177,8 @@ class LayerDesc(ctypes.Structure):
       + [("attn", SoftmaxAttnDesc), ("rec", RecurrentDesc), ("moe", MoeDesc), ("latent", LatentAttnDesc)]
       + [("conv_taps", ctypes.c_int32), ("residual_mult", ctypes.c_float)]
       + [(n, ctypes.c_void_p) for n in ("conv1", "conv2", "conv_state")]
+      + [(n, ctypes.c_int32) for n in ("side_dim", "side_col")]
+      + [(n, ctypes.c_void_p) for n in ("side_gate", "side_proj", "side_norm")]
   )
 
 
@@ -183,6 +191,7 @@ class LayeredConfig(ctypes.Structure):
       + [(n, ctypes.c_float) for n in ("eps", "embed_scale", "final_gain")]
       + [(n, ctypes.c_void_p) for n in ("embedding", "head", "final_norm")]
       + [("logit_softcap", ctypes.c_float), ("norm_groups", ctypes.c_int32), ("logit_scale", ctypes.c_float)]
+      + [("embed_norm", ctypes.c_void_p), ("side_embed", ctypes.c_void_p), ("side_width", ctypes.c_int32)]
   )
 
 

@@ -14,6 +14,10 @@
 //                           before a run's first come from the sequence's state (a ring of the last taps - 1 normed rows)
 //   conv_state_update_kernel  the last rows of every run go into that ring
 //   group_norm_rows_kernel  gnorm of a gathered subset of rows;  logit_post_kernel  z = cap * tanh(scale * z / cap)
+//   pre_norm_step_kernel    pre-norm layers: x = unit(x) * w0 (optional); x += y or x += unit(y) * wy (optional); a copy of x in the matmul
+//                           dtype (optional); unit(x) * w to the fp32 plane of normed rows and / or the matmul dtype (optional), or,
+//                           in steps of single tokens, straight through the next mixer's input convolution and into its ring
+//   side_act_kernel         act = gelu_tanh(gate) * table[token, col ..]: the gated rows of a per-layer token input
 //
 // Everything here is fp32 arithmetic; T is the dtype the matrix products and the cache use (bf16, or float for a float32 engine).
 #pragma once
@@ -185,7 +189,7 @@ struct InputConvArgs {
   const float* w2;       // the same for the second output, or null
   float* state;          // [slots, taps - 1, width]: the normed row of position p of a sequence at index p % (taps - 1)
   T* out1;               // [rows, width] h + conv1(h)
-  T* out2;               // [rows, width] h + conv2(h) (w2 null: h itself)
+  T* out2;               // [rows, width] h + conv2(h) (w2 null: h itself), or null: not written
   const int* group;
   const int* pos;
   int rows, width, taps;
@@ -218,7 +222,7 @@ __global__ void __launch_bounds__(256) group_norm_step_kernel(const float* y, fl
         if (cv.w2) s2 = fmaf(v, cv.w2[size_t(ring - back) * W + c], s2);
       }
       cv.out1[size_t(r) * W + c] = to_act<T>(hv + s1);
-      cv.out2[size_t(r) * W + c] = to_act<T>(hv + s2);
+      if (cv.out2) cv.out2[size_t(r) * W + c] = to_act<T>(hv + s2);
       if (ring > 0) cv.state[(size_t(grp) * ring + p % ring) * W + c] = hv;  // (the slot of position p - ring, read just above by this thread)
     }
   };
@@ -313,7 +317,7 @@ __global__ void __launch_bounds__(256) input_conv_kernel(const InputConvArgs<T> 
         if (a.w2) s2 = fmaf(v, a.w2[size_t(ring - back) * W + c], s2);
       }
       a.out1[size_t(r) * W + c] = to_act<T>(own + s1);
-      a.out2[size_t(r) * W + c] = to_act<T>(own + s2);
+      if (a.out2) a.out2[size_t(r) * W + c] = to_act<T>(own + s2);
     }
     return;
   }
@@ -328,18 +332,91 @@ __global__ void __launch_bounds__(256) input_conv_kernel(const InputConvArgs<T> 
       if (a.w2) s2 = fmaf(v, a.w2[size_t(ring - back) * W + c], s2);
     }
     a.out1[size_t(r) * W + c] = to_act<T>(own + s1);
-    a.out2[size_t(r) * W + c] = to_act<T>(own + s2);
+    if (a.out2) a.out2[size_t(r) * W + c] = to_act<T>(own + s2);
   }
 }
 
-// grid (runs, taps - 1): CTA (run, i) keeps the run's i-th row from its end, if the run is that long
+// grid (runs, taps - 1): CTA (run, i) keeps the run's i-th row from its end, if the run is that long (`ld`: row pitch of h)
 __global__ void __launch_bounds__(256) conv_state_update_kernel(const float* h, float* state, const int* run_row0, const int* group, const int* pos,
-                                                                int width, int taps) {
+                                                                int width, int taps, long long ld) {
   griddep_wait();
   const int r0 = run_row0[blockIdx.x], r1 = run_row0[blockIdx.x + 1], r = r1 - 1 - int(blockIdx.y), ring = taps - 1;
   if (r < r0) return;
   float* dst = state + (size_t(group[r]) * ring + pos[r] % ring) * width;
-  for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = h[size_t(r) * width + c];
+  for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = h[size_t(r) * ld + c];
+}
+
+struct PreNormArgs {
+  const float* y;       // [rows, width] joins x, or null
+  const float* y_w;     // [width]: x += unit(y) * y_w; null: x += y
+  const float* self_w;  // [width]: before anything else x = unit(x) * self_w (the norm of the embedding output); null: not
+  float* x;             // [rows, width]
+  const float* w;       // [width] weight of the norm that is written out; null: none is
+  float* h;             // [rows, width] unit(x) * w in fp32 (what an input convolution reads), or null
+  float eps;
+  int width;
+};
+
+// one CTA per row.  FUSED (steps in which every row is a single token of its own sequence): the normed values go straight through
+// the input convolution `cv` (the earlier rows come from the sequence's ring) and into the ring, with the arithmetic of
+// input_conv_kernel value by value.
+template <typename T, bool FUSED>
+__global__ void __launch_bounds__(256) pre_norm_step_kernel(const PreNormArgs a, T* x_copy, T* out, const InputConvArgs<T> cv) {
+  __shared__ float red[8];
+  griddep_wait();
+  const int r = blockIdx.x, W = a.width;
+  float* xr = a.x + size_t(r) * W;
+  const float* yr = a.y ? a.y + size_t(r) * W : nullptr;
+  float fy = 1.0f, fs = 1.0f;
+  if (yr && a.y_w) {
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < W; c += 256) ss = fmaf(yr[c], yr[c], ss);
+    fy = 1.0f / sqrtf(block_sum(ss, red) / float(W) + a.eps);
+  }
+  if (a.self_w) {
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < W; c += 256) ss = fmaf(xr[c], xr[c], ss);
+    fs = 1.0f / sqrtf(block_sum(ss, red) / float(W) + a.eps);
+  }
+  float ss2 = 0.0f;
+  for (int c = threadIdx.x; c < W; c += 256) {
+    float v = xr[c];
+    if (a.self_w) v = v * fs * a.self_w[c];
+    if (yr) v += a.y_w ? yr[c] * fy * a.y_w[c] : yr[c];
+    if (yr || a.self_w) xr[c] = v;
+    if (x_copy) x_copy[size_t(r) * W + c] = to_act<T>(v);
+    ss2 = fmaf(v, v, ss2);
+  }
+  if (!a.w) return;
+  const float f2 = 1.0f / sqrtf(block_sum(ss2, red) / float(W) + a.eps);
+  const int p = FUSED ? cv.pos[r] : 0, grp = FUSED ? cv.group[r] : 0, ring = cv.taps - 1;
+  for (int c = threadIdx.x; c < W; c += 256) {
+    const float hv = xr[c] * f2 * a.w[c];  // (xr[c]: this thread's own write above)
+    if constexpr (!FUSED) {
+      if (a.h) a.h[size_t(r) * W + c] = hv;
+      if (out) out[size_t(r) * W + c] = to_act<T>(hv);
+    } else {
+      float s1 = hv * cv.w1[size_t(ring) * W + c];
+      for (int back = 1; back <= ring && back <= p; ++back)
+        s1 = fmaf(cv.state[(size_t(grp) * ring + (p - back) % ring) * W + c], cv.w1[size_t(ring - back) * W + c], s1);
+      cv.out1[size_t(r) * W + c] = to_act<T>(hv + s1);
+      if (ring > 0) cv.state[(size_t(grp) * ring + p % ring) * W + c] = hv;  // (the slot of position p - ring, read just above by this thread)
+    }
+  }
+}
+
+// act[r, c] = gelu_tanh(gate[r, c]) * table[token[r], col + c], c < dim
+template <typename T>
+__global__ void __launch_bounds__(256) side_act_kernel(const float* gate, long long ld_gate, const int* token, const T* table, long long ld_table, int col,
+                                                       int vocab, T* act, int dim, long long total) {
+  griddep_wait();
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / dim;
+    const int c = int(i % dim);
+    int tok = token[r];
+    tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
+    act[i] = to_act<T>(gelu_tanh_f(gate[r * ld_gate + c]) * act_f32(table[size_t(tok) * ld_table + col + c]));
+  }
 }
 
 template <typename T>

@@ -55,6 +55,10 @@ struct mtx_layered {
   int max_lat_q = 0, max_lat_o = 0;
   float *h = nullptr, *lat_q = nullptr;
   void *xb = nullptr, *lat_o = nullptr;
+  // MTX_NORM_PRE layers (they share h and xb with the parallel ones): the output gate of a recurrence whose gate is low-rank
+  bool prenorm = false;
+  int max_rec_gate = 0;
+  float* rec_gate = nullptr;
 };
 
 namespace {
@@ -64,7 +68,7 @@ size_t elem(const mtx_layered* e) { return e->cfg.float32 ? 4 : 2; }
 struct LWs {
   size_t x, y, qkv, v_shared, xa, q, attn, act, wanted, obf, attn_part, total;
   size_t smax_ml, x0, rec_o, rec_aux, moe_logits, moe_weight, moe_y, moe_chosen, moe_slot, moe_row, moe_off, moe_act;
-  size_t h, xb, lat_q, lat_o;
+  size_t h, xb, lat_q, lat_o, rec_gate;
 };
 
 LWs layered_layout(const mtx_layered* e) {
@@ -102,8 +106,9 @@ LWs layered_layout(const mtx_layered* e) {
   L.moe_row = take((RT + 1) * 4);
   L.moe_off = take(size_t(e->max_moe_experts + 2) * 4);
   L.moe_act = take((RT * size_t(e->max_moe_ff) + 1) * es);
-  L.h = take(e->parallel ? R * c.width * 4 : 4);
-  L.xb = take(e->parallel ? R * c.width * es : 4);
+  L.h = take(e->parallel || e->prenorm ? R * c.width * 4 : 4);
+  L.xb = take(e->parallel || e->prenorm ? R * c.width * es : 4);
+  L.rec_gate = take(R * size_t(e->max_rec_gate > 0 ? e->max_rec_gate : 1) * 4);
   L.lat_q = take(R * size_t(e->max_lat_q > 0 ? e->max_lat_q : 1) * 4);
   L.lat_o = take(R * size_t(e->max_lat_o > 0 ? e->max_lat_o : 1) * es);
   L.total = off;
@@ -123,13 +128,13 @@ __global__ void bf16_rows_to_f32_kernel(const bf16* src, const float* bias, floa
     dst[i] = __bfloat162float(src[i]) + (bias ? bias[i % n] : 0.0f);
 }
 
-// (limit > 0: the clamped form g sigmoid(1.702 g) (u + 1); else gelu_tanh(g) u)
-__global__ void gate_up_bf16_kernel(const bf16* src, bf16* act, int ff, long long total, float limit) {
+// (mode 0: gelu_tanh(g) u; 1: the clamped form g sigmoid(1.702 g) (u + 1); 2: silu(g) u)
+__global__ void gate_up_bf16_kernel(const bf16* src, bf16* act, int ff, long long total, float limit, int mode) {
   griddep_wait();
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const long long r = i / ff, f = i % ff;
     const float g = __bfloat162float(src[r * 2 * ff + 2 * f]), u = __bfloat162float(src[r * 2 * ff + 2 * f + 1]);
-    act[i] = __float2bfloat16_rn(limit > 0.0f ? clamped_gate_f(g, u, limit) : gelu_tanh_f(g) * u);
+    act[i] = __float2bfloat16_rn(mode == 1 ? clamped_gate_f(g, u, limit) : (mode == 2 ? silu_gate_f(g, u) : gelu_tanh_f(g) * u));
   }
 }
 
@@ -195,7 +200,8 @@ int run_linear_umma(mtx_layered* e, const void* a, const void* w, const float* b
   if (EPI == LIN_ACT || EPI == LIN_RELU2)
     return launch(act_bf16_kernel, dim3(blocks), dim3(256), 0, st, tmp, static_cast<bf16*>(act), n, ldo > 0 ? ldo : (long long)n, total, EPI == LIN_RELU2 ? 1 : 0);
   if (gated)
-    return launch(gate_up_bf16_kernel, dim3(blocks), dim3(256), 0, st, tmp, static_cast<bf16*>(act), n / 2, total, EPI == LIN_GATED_CLAMP ? limit : 0.0f);
+    return launch(gate_up_bf16_kernel, dim3(blocks), dim3(256), 0, st, tmp, static_cast<bf16*>(act), n / 2, total, limit,
+                  EPI == LIN_GATED_CLAMP ? (limit > 0.0f ? 1 : 2) : 0);
   return launch(bf16_rows_to_f32_kernel, dim3(blocks), dim3(256), 0, st, tmp, bias, out, n, total);
 }
 
@@ -529,7 +535,7 @@ int launch_rec_scan_t(const RecScanArgs& ra, dim3 grid, dim3 block, size_t smem,
 template <int KIND, int CB, int SL>
 int launch_rec_scan_cb(const RecScanArgs& ra, int n_runs, cudaStream_t st) {
   const dim3 grid(n_runs, ra.heads, (ra.vdim + CB - 1) / CB), block(CB * SL);
-  const size_t smem = rec_scan_smem_bytes(ra.dim, CB, SL, ra.chunk, KIND == REC_DELTA ? 5 : 3);
+  const size_t smem = rec_scan_smem_bytes(ra.dim, CB, SL, ra.chunk, KIND == REC_DELTA ? 5 : 3);  // (the gated delta rule stages q, k, decays)
   const int rpt = rec_rpt(ra.dim, SL);
   if (rpt == 4) return launch_rec_scan_t<KIND, 4, CB, SL>(ra, grid, block, smem, st);
   if (rpt == 8) return launch_rec_scan_t<KIND, 8, CB, SL>(ra, grid, block, smem, st);
@@ -972,7 +978,7 @@ int parallel_layer(mtx_layered* e, int li, const mtx_ragged_batch& b, cudaStream
     MTX_TRY(launch(input_conv_kernel<T>, dim3(rows), dim3(256), 0, st, input_conv_args<T>(e, l, b)));
     if (l.conv_taps > 1)
       MTX_TRY(launch(conv_state_update_kernel, dim3(b.n_runs, l.conv_taps - 1), dim3(256), 0, st, (const float*)e->h, l.conv_state, b.run_row0, b.group, b.pos, E,
-                     l.conv_taps));
+                     l.conv_taps, (long long)E));
   }
   MTX_TRY((linear<T, LIN_PLAIN>(e, xa, l.w_in, nullptr, e->qkv, nullptr, rows, n_in, E, st)));
   SoftmaxAttnArgs<T> sa;
@@ -1155,6 +1161,303 @@ int parallel_layer(mtx_layered* e, int li, const mtx_ragged_batch& b, cudaStream
   return group_norm_step<T>(e, e->y, l.residual_mult, li + 1, b, st);
 }
 
+// Column layout of a MTX_NORM_PRE layer's input projection.
+struct PreCols {
+  int aq = 0, ak = 0, av = 0;                           // softmax attention: q, k, v
+  int rq = 0, rb = 0, ra = 0, rg = 0;                   // gated delta rule: q | k | v from rq, write strengths, the decay's input, the gate's input
+  int n = 0, k_mix = 0;
+};
+
+PreCols pre_cols(const mtx_layer_desc& l) {
+  PreCols pc;
+  const mtx_softmax_attn_desc& a = l.attn;
+  const mtx_recurrent_desc& r = l.rec;
+  int at = 0;
+  if (a.heads > 0) {
+    pc.aq = at;
+    at += a.heads * a.dim;
+    if (!a.shared_kv) {
+      pc.ak = at;
+      at += a.kv_heads * a.dim;
+      pc.av = at;
+      at += a.kv_heads * a.vdim;
+    }
+    pc.k_mix = a.heads * a.vdim;
+  } else {
+    const int G = r.kv_heads > 0 ? r.kv_heads : r.heads;
+    pc.rq = at;
+    at += 2 * G * r.dim + r.heads * r.vdim;
+    pc.rb = at;
+    at += r.heads;
+    pc.ra = at;
+    at += r.decay_rank > 0 ? r.decay_rank : r.heads;
+    pc.rg = at;
+    at += r.gate_rank > 0 ? r.gate_rank : r.heads * r.vdim;
+    pc.k_mix = r.heads * r.vdim;
+  }
+  pc.n = at;
+  return pc;
+}
+
+// MTX_NORM_PRE: x += y (or unit(y) * y_w; y null: no update), optionally a copy of x in the matmul dtype to xb, then unit(x) * w:
+// `next` >= 0: the norm before layer `next`'s mixer (none after the last layer), to the plane h, or -- in steps of single tokens --
+// straight through that layer's input convolution into xa; `next` < 0: the norm `w` before a feed-forward, to xa
+template <typename T>
+int pre_norm_step(mtx_layered* e, const float* y, const float* y_w, const float* self_w, bool copy_x, int next, const float* w, const mtx_ragged_batch& b,
+                  cudaStream_t st) {
+  PreNormArgs pa;
+  memset(&pa, 0, sizeof(pa));
+  pa.y = y;
+  pa.y_w = y_w;
+  pa.self_w = self_w;
+  pa.x = e->x;
+  pa.eps = e->cfg.eps;
+  pa.width = e->cfg.width;
+  T* xc = copy_x ? static_cast<T*>(e->xb) : nullptr;
+  InputConvArgs<T> cv;
+  memset(&cv, 0, sizeof(cv));
+  if (next >= 0) {
+    if (next >= e->cfg.num_layers) {
+      if (!y && !self_w && !copy_x) return MTX_OK;
+      return launch(pre_norm_step_kernel<T, false>, dim3(b.rows), dim3(256), 0, st, pa, xc, (T*)nullptr, cv);
+    }
+    const mtx_layer_desc& nl = e->layers[next];
+    pa.w = nl.norm1;
+    if (single_token_rows(b)) {
+      cv = input_conv_args<T>(e, nl, b);
+      cv.w2 = nullptr;
+      cv.out2 = nullptr;
+      return launch(pre_norm_step_kernel<T, true>, dim3(b.rows), dim3(256), 0, st, pa, xc, (T*)nullptr, cv);
+    }
+    pa.h = e->h;
+    return launch(pre_norm_step_kernel<T, false>, dim3(b.rows), dim3(256), 0, st, pa, xc, (T*)nullptr, cv);
+  }
+  pa.w = w;
+  return launch(pre_norm_step_kernel<T, false>, dim3(b.rows), dim3(256), 0, st, pa, xc, static_cast<T*>(e->xa), cv);
+}
+
+// a MTX_NORM_PRE layer; h holds unit(x) * norm1 on entry (steps of single tokens: xa already holds the mixer's input)
+template <typename T>
+int prenorm_layer(mtx_layered* e, int li, const mtx_ragged_batch& b, cudaStream_t st) {
+  const mtx_layered_config& c = e->cfg;
+  const mtx_layer_desc& l = e->layers[li];
+  const int rows = b.rows, E = c.width;
+  T* xa = static_cast<T*>(e->xa);
+  const PreCols pc = pre_cols(l);
+  const int n_in = l.n_in;
+  T* mix = static_cast<T*>(e->attn);  // [rows, k_mix]
+  if (!single_token_rows(b)) {  // (else the kernel that normed the rows has done this too)
+    InputConvArgs<T> ca = input_conv_args<T>(e, l, b);
+    ca.w2 = nullptr;
+    ca.out2 = nullptr;
+    MTX_TRY(launch(input_conv_kernel<T>, dim3(rows), dim3(256), 0, st, ca));
+    if (l.conv_taps > 1)
+      MTX_TRY(launch(conv_state_update_kernel, dim3(b.n_runs, l.conv_taps - 1), dim3(256), 0, st, (const float*)e->h, l.conv_state, b.run_row0, b.group, b.pos, E,
+                     l.conv_taps, (long long)E));
+  }
+  MTX_TRY((linear<T, LIN_PLAIN>(e, xa, l.w_in, nullptr, e->qkv, nullptr, rows, n_in, E, st)));
+  if (l.attn.heads > 0) {
+    const mtx_softmax_attn_desc& a = l.attn;
+    QkPrepareArgs<T> qa;
+    memset(&qa, 0, sizeof(qa));
+    qa.proj = e->qkv;
+    qa.ld = n_in;
+    qa.q_col = pc.aq;
+    qa.k_col = pc.ak;
+    qa.v_col = pc.av;
+    qa.q_norm = a.q_norm;
+    qa.k_norm = a.k_norm;
+    qa.norm_whole = a.norm_whole;
+    qa.rot_freq = a.rot_freq;
+    qa.q_out = static_cast<T*>(e->q);
+    qa.k_pages = static_cast<T*>(a.k_pages);
+    qa.v_pages = static_cast<T*>(a.v_pages);
+    qa.group = b.group;
+    qa.pos = b.pos;
+    qa.page_map = b.page_map;
+    qa.heads = a.heads;
+    qa.kv_heads = a.kv_heads;
+    qa.dim = a.dim;
+    qa.vdim = a.vdim;
+    qa.rot_dims = a.rot_dims;
+    qa.rot_half = a.rot_half;
+    qa.shared_kv = a.shared_kv;
+    qa.num_pages = c.num_pages;
+    qa.tokens_per_page = c.tokens_per_page;
+    qa.max_pages = c.max_pages_per_group;
+    qa.eps = c.eps;
+    MTX_TRY(launch(qk_prepare_append_kernel<T>, dim3(rows), dim3(256), 0, st, qa));
+    if (a.pool > 0 && !a.pool_shared) {  // the blocks that this step's rows complete
+      PoolAppendArgs<T> pa;
+      memset(&pa, 0, sizeof(pa));
+      pa.k_pages = static_cast<const T*>(a.k_pages);
+      pa.v_pages = static_cast<const T*>(a.v_pages);
+      pa.kp_pages = static_cast<T*>(a.kp_pages);
+      pa.vp_pages = static_cast<T*>(a.vp_pages);
+      pa.group = b.group;
+      pa.pos = b.pos;
+      pa.page_map = b.page_map;
+      pa.kv_heads = a.kv_heads;
+      pa.dim = a.dim;
+      pa.vdim = a.vdim;
+      pa.pool = a.pool;
+      pa.pool_slots = a.pool_slots;
+      pa.num_pages = c.num_pages;
+      pa.tokens_per_page = c.tokens_per_page;
+      pa.max_pages = c.max_pages_per_group;
+      MTX_TRY(launch(pool_append_kernel<T>, dim3(rows), dim3(256), 0, st, pa));
+    }
+    SoftmaxAttnArgs<T> sa;
+    memset(&sa, 0, sizeof(sa));
+    sa.group = b.group;
+    sa.pos = b.pos;
+    sa.page_map = b.page_map;
+    sa.tile_row0 = b.tile_row0;
+    sa.num_pages = c.num_pages;
+    sa.tokens_per_page = c.tokens_per_page;
+    sa.max_pages = c.max_pages_per_group;
+    sa.out_scale = a.out_scale != 0.0f ? a.out_scale : 1.0f;
+    sa.splits = 1;
+    sa.rows = rows;
+    sa.q = static_cast<const T*>(e->q);
+    sa.out = mix;
+    sa.ld_out = pc.k_mix;
+    sa.k_pages = static_cast<const T*>(a.k_pages);
+    sa.v_pages = static_cast<const T*>(a.v_pages);
+    sa.heads = a.heads;
+    sa.kv_heads = a.kv_heads;
+    sa.dim = a.dim;
+    sa.vdim = a.vdim;
+    sa.window = a.window;
+    sa.scale = a.scale;
+    sa.slopes = a.slopes;
+    sa.sink = a.sink;
+    sa.softcap = a.softcap;
+    sa.pool = a.pool;
+    sa.pool_slots = a.pool_slots;
+    sa.kp_pages = static_cast<const T*>(a.kp_pages);
+    sa.vp_pages = static_cast<const T*>(a.vp_pages);
+    MTX_TRY(run_softmax_attention<T>(e, sa, b, st));
+  } else {
+    const mtx_recurrent_desc& r = l.rec;
+    const int G = r.kv_heads > 0 ? r.kv_heads : r.heads, C = 2 * G * r.dim + r.heads * r.vdim;
+    const GDeltaCols gc = gdelta_cols(r.heads, G, r.dim, r.vdim);
+    GDeltaPrepareArgs<T> ga;
+    memset(&ga, 0, sizeof(ga));
+    ga.proj = e->qkv + pc.rq;
+    ga.ld = n_in;
+    ga.b_col = pc.rb - pc.rq;
+    ga.a_col = pc.ra - pc.rq;
+    ga.g_col = pc.rg - pc.rq;
+    ga.heads = r.heads;
+    ga.kv_heads = G;
+    ga.dim = r.dim;
+    ga.vdim = r.vdim;
+    ga.taps = r.conv_taps;
+    ga.rank = r.decay_rank;
+    ga.gate_rank = r.gate_rank;
+    ga.key_eps = r.key_eps;
+    ga.conv_w = r.conv_w;
+    ga.state = r.conv_state;
+    ga.a_log = r.a_log;
+    ga.bias = r.decay_bias;
+    ga.up_t = r.decay_up_t;
+    ga.group = b.group;
+    ga.pos = b.pos;
+    ga.out = e->rec_aux;
+    ga.gate_low = r.gate_rank > 0 ? static_cast<T*>(e->act) : nullptr;
+    MTX_TRY(launch(gdelta_prepare_kernel<T>, dim3(rows), dim3(256), sizeof(float) * (C + r.decay_rank), st, ga));
+    if (r.conv_taps > 1)
+      MTX_TRY(launch(conv_state_update_kernel, dim3(b.n_runs, r.conv_taps - 1), dim3(256), 0, st, (const float*)(e->qkv + pc.rq), r.conv_state, b.run_row0, b.group,
+                     b.pos, C, r.conv_taps, (long long)n_in));
+    if (r.gate_rank > 0)
+      MTX_TRY((linear<T, LIN_PLAIN>(e, e->act, r.w_gate_up, nullptr, e->rec_gate, nullptr, rows, r.heads * r.vdim, r.gate_rank, st)));
+    RecScanArgs ra;
+    memset(&ra, 0, sizeof(ra));
+    ra.proj = e->rec_aux;
+    ra.ld = gc.n;
+    ra.q_col = gc.q;
+    ra.k_col = gc.k;
+    ra.v_col = gc.v;
+    ra.aux = e->rec_aux;
+    ra.aux_ld = gc.n;
+    ra.dec_col = gc.decay;
+    ra.beta_col = gc.beta;
+    ra.qk_rep = r.heads / G;
+    ra.o = e->rec_o;
+    ra.state_s = r.state_s;
+    ra.run_row0 = b.run_row0;
+    ra.group = b.group;
+    ra.pos = b.pos;
+    ra.heads = r.heads;
+    ra.dim = r.dim;
+    ra.vdim = r.vdim;
+    ra.q_scale = r.q_scale;
+    ra.vec4 = (r.dim % 4 == 0 && r.vdim % 4 == 0) ? 1 : 0;  // (the plane's parts start on multiples of four floats)
+    MTX_TRY(launch_rec_scan<REC_GDELTA>(e, ra, b.n_runs, rows, st));
+    RecOutArgs<T> oa;
+    memset(&oa, 0, sizeof(oa));
+    oa.o = e->rec_o;
+    oa.proj = r.gate_rank > 0 ? e->rec_gate : e->qkv;
+    oa.ld = r.gate_rank > 0 ? r.heads * r.vdim : n_in;
+    oa.g_col = r.gate_rank > 0 ? 0 : pc.rg;
+    oa.weight = r.out_norm;
+    oa.out = mix;
+    oa.ld_out = pc.k_mix;
+    oa.out_col = 0;
+    oa.heads = r.heads;
+    oa.vdim = r.vdim;
+    oa.gate_silu = r.gate_silu;
+    oa.eps = c.eps;
+    oa.out_scale = r.out_scale != 0.0f ? r.out_scale : 1.0f;
+    MTX_TRY(launch(recurrent_out_kernel<T>, dim3(rows), dim3(256), 0, st, oa));
+  }
+  MTX_TRY((linear<T, LIN_PLAIN>(e, mix, l.wo, nullptr, e->y, nullptr, rows, E, pc.k_mix, st)));
+  const mtx_moe_desc& m = l.moe;
+  const bool has_ff = m.experts > 0, has_side = l.side_dim > 0;
+  if (has_ff) {
+    MTX_TRY(pre_norm_step<T>(e, e->y, nullptr, nullptr, false, -1, l.norm2, b, st));  // x += mixer; xa = unit(x) * norm2
+    const int entries = rows * m.top;
+    const float limit = m.act_silu ? 0.0f : m.limit, shared_limit = m.act_silu ? 0.0f : m.shared_limit;
+    MTX_TRY((linear<T, LIN_PLAIN>(e, xa, m.w_router, nullptr, e->moe_logits, nullptr, rows, m.experts, E, st)));
+    MoeRouteArgs ra;
+    memset(&ra, 0, sizeof(ra));
+    ra.logits = e->moe_logits;
+    ra.correction = m.correction;
+    ra.chosen = e->moe_chosen;
+    ra.weight = e->moe_weight;
+    ra.experts = m.experts;
+    ra.top = m.top;
+    ra.groups = m.groups > 0 ? m.groups : 1;
+    ra.keep = m.keep_groups > 0 ? m.keep_groups : 1;
+    ra.softmax = m.score_softmax;
+    ra.plain = m.plain_weights;
+    MTX_TRY(launch(moe_route_kernel, dim3(rows), dim3(32), sizeof(float) * (2 * m.experts + ra.groups), st, ra));
+    MTX_TRY(launch(moe_sort_kernel, dim3(1), dim3(1024), sizeof(int) * (2 * m.experts + 1), st, (const int*)e->moe_chosen, entries, m.top, m.experts,
+                   e->moe_off, e->moe_slot, e->moe_row));
+    MTX_TRY((linear_grouped<T, LIN_GATED_CLAMP>(xa, e->moe_row, m.w_gate_up, (long long)2 * m.ff * E, e->moe_off, m.experts, nullptr, e->moe_act, entries,
+                                                2 * m.ff, E, limit, st)));
+    MTX_TRY((linear_grouped<T, LIN_PLAIN>(e->moe_act, nullptr, m.w_down, (long long)E * m.ff, e->moe_off, m.experts, e->moe_y, nullptr, entries, E, m.ff,
+                                          0.0f, st)));
+    if (m.shared_ff > 0) {
+      MTX_TRY((linear<T, LIN_GATED_CLAMP>(e, xa, m.shared_gate_up, nullptr, nullptr, e->act, rows, 2 * m.shared_ff, E, st, shared_limit)));
+      MTX_TRY((linear<T, LIN_PLAIN>(e, e->act, m.shared_down, nullptr, e->y, nullptr, rows, E, m.shared_ff, st)));
+    }
+    MTX_TRY(launch(moe_combine_kernel, dim3(rows), dim3(256), 0, st, (const float*)e->moe_y, (const int*)e->moe_slot, (const float*)e->moe_weight, m.top, E,
+                   m.shared_ff > 0 ? 1 : 0, e->y));
+  }
+  if (!has_side) return pre_norm_step<T>(e, e->y, nullptr, nullptr, false, li + 1, nullptr, b, st);  // x += the last sublayer; the next layer's norm
+  // x += the last sublayer, and x in the matmul dtype for the side input's gate
+  MTX_TRY(pre_norm_step<T>(e, e->y, nullptr, nullptr, true, c.num_layers, nullptr, b, st));
+  MTX_TRY((linear<T, LIN_PLAIN>(e, e->xb, l.side_gate, nullptr, e->qkv, nullptr, rows, l.side_dim, E, st)));
+  const long long total = (long long)rows * l.side_dim;
+  const int blocks = int((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+  MTX_TRY(launch(side_act_kernel<T>, dim3(blocks), dim3(256), 0, st, (const float*)e->qkv, (long long)l.side_dim, b.token, static_cast<const T*>(c.side_embed),
+                 (long long)c.side_width, l.side_col, c.vocab, static_cast<T*>(e->act), l.side_dim, total));
+  MTX_TRY((linear<T, LIN_PLAIN>(e, e->act, l.side_proj, nullptr, e->y, nullptr, rows, E, l.side_dim, st)));
+  return pre_norm_step<T>(e, e->y, l.side_norm, nullptr, false, li + 1, nullptr, b, st);  // x += unit(y) * side_norm; the next layer's norm
+}
+
 template <typename T>
 int step_typed(mtx_layered* e, const mtx_ragged_batch& b, cudaStream_t st) {
   const mtx_layered_config& c = e->cfg;
@@ -1164,14 +1467,18 @@ int step_typed(mtx_layered* e, const mtx_ragged_batch& b, cudaStream_t st) {
                  e->sandwich ? e->x0 : (float*)nullptr));
   if (e->sandwich) MTX_TRY(sandwich_step<T>(e, nullptr, nullptr, nullptr, nullptr, 0, rows, st));  // layer 0's pre-adds and pre-norm
   if (e->parallel) MTX_TRY(group_norm_step<T>(e, nullptr, 0.0f, 0, b, st));                         // layer 0's norm
+  if (e->prenorm) MTX_TRY(pre_norm_step<T>(e, nullptr, nullptr, c.embed_norm, false, 0, nullptr, b, st));  // the embedding's norm, layer 0's norm
   for (int li = 0; li < c.num_layers; ++li) {
-    if (e->layers[li].norm_style == MTX_NORM_PARALLEL) MTX_TRY(parallel_layer<T>(e, li, b, st));
+    if (e->layers[li].norm_style == MTX_NORM_PRE) MTX_TRY(prenorm_layer<T>(e, li, b, st));
+    else if (e->layers[li].norm_style == MTX_NORM_PARALLEL) MTX_TRY(parallel_layer<T>(e, li, b, st));
     else if (e->layers[li].mixer == MTX_MIXER_COMPOSITE) MTX_TRY(composite_layer<T>(e, li, b, st));
     else MTX_TRY(window_layer<T>(e, li, b, st));
   }
   if (b.n_want > 0) {
     T* wn = static_cast<T*>(e->wanted);
-    if (e->parallel) MTX_TRY(launch(group_norm_rows_kernel<T>, dim3(b.n_want), dim3(256), 0, st, (const float*)e->x, b.want_rows, c.final_norm, c.eps, wn, E, c.norm_groups));
+    if (e->parallel || e->prenorm)
+      MTX_TRY(launch(group_norm_rows_kernel<T>, dim3(b.n_want), dim3(256), 0, st, (const float*)e->x, b.want_rows, c.final_norm, c.eps, wn, E,
+                     e->prenorm ? 1 : c.norm_groups));
     else if (c.final_norm) MTX_TRY(launch(weighted_norm_rows_kernel<T>, dim3(b.n_want), dim3(256), 0, st, (const float*)e->x, b.want_rows, c.final_norm, c.eps, wn, E));
     else MTX_TRY(launch(scalar_norm_rows_kernel<T>, dim3(b.n_want), dim3(256), 0, st, (const float*)e->x, b.want_rows, c.final_gain, c.eps, wn, E));
     MTX_TRY((linear<T, LIN_PLAIN>(e, wn, c.head, nullptr, b.logits, nullptr, b.n_want, c.vocab, E, st)));
@@ -1299,6 +1606,80 @@ int check_parallel(mtx_layered* e, int i) {
   return MTX_OK;
 }
 
+// validation and workspace sizes of a MTX_NORM_PRE layer
+int check_prenorm(mtx_layered* e, int i) {
+  const mtx_layered_config& c = e->cfg;
+  const mtx_layer_desc& l = e->layers[i];
+  const mtx_softmax_attn_desc& a = l.attn;
+  const mtx_recurrent_desc& r = l.rec;
+  const mtx_moe_desc& m = l.moe;
+  if (l.mixer != MTX_MIXER_COMPOSITE) return fail(MTX_ERR_UNSUPPORTED, "layer %d: a pre-norm layer has a composite mixer", i);
+  if (!l.norm1 || !l.w_in || !l.wo) return fail(MTX_ERR_ARG, "layer %d: the norm weight or a projection is missing", i);
+  if (l.conv_taps < 1 || !l.conv1 || (l.conv_taps > 1 && !l.conv_state)) return fail(MTX_ERR_ARG, "layer %d: the input convolution's taps / weights / state", i);
+  if ((a.heads > 0) + (r.kind != 0) != 1 || l.latent.heads > 0) return fail(MTX_ERR_ARG, "layer %d: a pre-norm layer has one mixer, an attention or a recurrence", i);
+  if (a.heads > 0) {
+    if (a.kv_heads < 1 || a.heads % a.kv_heads != 0 || a.dim < 1 || a.vdim < 1 || a.window < 0) return fail(MTX_ERR_ARG, "layer %d: bad attention geometry", i);
+    if (a.rot_dims < 0 || a.rot_dims > a.dim || (a.rot_dims & 1) || (a.rot_dims > 0 && !a.rot_freq)) return fail(MTX_ERR_ARG, "layer %d: bad rot_dims / rot_freq", i);
+    if (a.values_are_keys || a.head_gate) return fail(MTX_ERR_UNSUPPORTED, "layer %d: values_are_keys / head gates belong to other layer styles", i);
+    if (!a.k_pages || !a.v_pages) return fail(MTX_ERR_ARG, "layer %d: a page pool is missing", i);
+    if (a.pool < 0 || (a.pool > 0 && (a.window < 1 || a.pool_slots < 1 || !a.kp_pages || !a.vp_pages || a.k_pages == a.v_pages || a.slopes)))
+      return fail(MTX_ERR_ARG, "layer %d: pooled blocks need a window, their pools, and no distance slopes", i);
+    if (a.pool > 0 && !(c.tokens_per_page % a.pool == 0 ? a.pool_slots == c.tokens_per_page / a.pool : a.pool_slots == c.tokens_per_page))
+      return fail(MTX_ERR_ARG, "layer %d: pool_slots = %d does not fit pages of %d tokens and blocks of %d", i, a.pool_slots, c.tokens_per_page, a.pool);
+    if (kSmaxRows * a.vdim > kSmaxThreads * kSmaxMaxAcc) return fail(MTX_ERR_UNSUPPORTED, "layer %d: vdim %d exceeds %d", i, a.vdim, kSmaxThreads * kSmaxMaxAcc / kSmaxRows);
+    if (softmax_attn_smem_bytes(a.dim, a.vdim) > 200 * 1024) return fail(MTX_ERR_UNSUPPORTED, "layer %d: the attention's heads do not fit shared memory", i);
+    if (a.heads * a.dim > e->max_qdim) e->max_qdim = a.heads * a.dim;
+    if (a.heads > e->max_attn_heads) e->max_attn_heads = a.heads;
+  } else {
+    if (r.kind != MTX_REC_GDELTA) return fail(MTX_ERR_UNSUPPORTED, "layer %d: a pre-norm layer's recurrence is the gated delta rule", i);
+    const int G = r.kv_heads > 0 ? r.kv_heads : r.heads;
+    if (r.heads < 1 || r.heads % G != 0 || r.dim < 1 || r.vdim < 1 || r.dim > kRecSlices * 32)
+      return fail(MTX_ERR_UNSUPPORTED, "layer %d: recurrence heads / kv_heads / dim (<= %d) / vdim", i, kRecSlices * 32);
+    if (!r.state_s || !r.out_norm || !r.a_log || !r.decay_bias || !r.conv_w || r.conv_taps < 1 || (r.conv_taps > 1 && !r.conv_state))
+      return fail(MTX_ERR_ARG, "layer %d: the recurrence's state, output norm, decay constants or convolution is missing", i);
+    if (r.decay_rank < 0 || r.gate_rank < 0 || (r.decay_rank > 0 && !r.decay_up_t) || (r.gate_rank > 0 && !r.w_gate_up))
+      return fail(MTX_ERR_ARG, "layer %d: a low-rank decay / gate needs its up-projection", i);
+    const size_t smem = sizeof(float) * size_t(2 * G * r.dim + r.heads * r.vdim + r.decay_rank);
+    if (smem > 200 * 1024) return fail(MTX_ERR_UNSUPPORTED, "layer %d: the recurrence's projections do not fit shared memory", i);
+    if (smem > 48 * 1024) {
+      const cudaError_t e1 = cudaFuncSetAttribute(gdelta_prepare_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+      const cudaError_t e2 = cudaFuncSetAttribute(gdelta_prepare_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+      if (e1 != cudaSuccess || e2 != cudaSuccess) cudaGetLastError();  // (no device: the create call only validates)
+    }
+    if (r.heads * r.vdim > e->max_rec_o) e->max_rec_o = r.heads * r.vdim;
+    const int aux = gdelta_cols(r.heads, G, r.dim, r.vdim).n;
+    if (aux > e->max_rec_aux) e->max_rec_aux = aux;
+    if (r.gate_rank > 0 && r.heads * r.vdim > e->max_rec_gate) e->max_rec_gate = r.heads * r.vdim;
+    if (r.gate_rank > e->max_ff) e->max_ff = r.gate_rank;  // (the low-rank gate's input waits in the plane of the feed-forward's activation)
+  }
+  const PreCols pc = pre_cols(l);
+  if (l.n_in < pc.n) return fail(MTX_ERR_ARG, "layer %d: n_in = %d, the mixer needs %d projection rows", i, l.n_in, pc.n);
+  if (l.n_in > e->max_nqkv) e->max_nqkv = l.n_in;
+  if (pc.k_mix > e->max_odim) e->max_odim = pc.k_mix;
+  if (m.experts > 0) {
+    if (l.ff_kind != MTX_FF_MOE || !l.norm2) return fail(MTX_ERR_ARG, "layer %d: a pre-norm layer's feed-forward is a routed one with a norm weight", i);
+    const int groups = m.groups > 0 ? m.groups : 1, keep = m.keep_groups > 0 ? m.keep_groups : 1;
+    if (m.top < 1 || m.top > m.experts || m.experts % groups != 0 || keep > groups || m.ff < 1 || keep * (m.experts / groups) < m.top)
+      return fail(MTX_ERR_ARG, "layer %d: bad expert / top / groups / ff", i);
+    if (m.experts > 4096) return fail(MTX_ERR_UNSUPPORTED, "layer %d: more than 4096 experts", i);
+    if (!m.w_router || !m.w_gate_up || !m.w_down || (m.shared_ff > 0 && (!m.shared_gate_up || !m.shared_down))) return fail(MTX_ERR_ARG, "layer %d: an expert weight is missing", i);
+    if (m.top > e->max_moe_top) e->max_moe_top = m.top;
+    if (m.experts > e->max_moe_experts) e->max_moe_experts = m.experts;
+    if (m.ff > e->max_moe_ff) e->max_moe_ff = m.ff;
+    if (m.shared_ff > e->max_ff) e->max_ff = m.shared_ff;
+    if (2 * m.shared_ff > e->max_nqkv) e->max_nqkv = 2 * m.shared_ff;
+  }
+  if (l.side_dim < 0) return fail(MTX_ERR_ARG, "layer %d: side_dim", i);
+  if (l.side_dim > 0) {
+    if (!l.side_gate || !l.side_proj || !l.side_norm || !c.side_embed || l.side_col < 0 || l.side_col + l.side_dim > c.side_width)
+      return fail(MTX_ERR_ARG, "layer %d: the side input's weights, table or columns are missing", i);
+    if (l.side_dim > e->max_ff) e->max_ff = l.side_dim;
+    if (l.side_dim > e->max_nqkv) e->max_nqkv = l.side_dim;
+  }
+  e->prenorm = true;
+  return MTX_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -1316,8 +1697,8 @@ int mtx_layered_create(const mtx_layered_config* cfg, const mtx_layer_desc* laye
   for (int i = 0; i < c.num_layers; ++i) {
     const mtx_layer_desc& l = e->layers[i];
     int rc = MTX_OK;
-    if (l.norm_style == MTX_NORM_PARALLEL || l.mixer == MTX_MIXER_COMPOSITE) {
-      rc = l.norm_style == MTX_NORM_PARALLEL ? check_parallel(e, i) : check_composite(e, i);
+    if (l.norm_style == MTX_NORM_PARALLEL || l.norm_style == MTX_NORM_PRE || l.mixer == MTX_MIXER_COMPOSITE) {
+      rc = l.norm_style == MTX_NORM_PRE ? check_prenorm(e, i) : (l.norm_style == MTX_NORM_PARALLEL ? check_parallel(e, i) : check_composite(e, i));
       if (rc != MTX_OK) {
         delete e;
         return rc;
@@ -1364,9 +1745,14 @@ int mtx_layered_create(const mtx_layered_config* cfg, const mtx_layer_desc* laye
       delete e;
       return fail(MTX_ERR_UNSUPPORTED, "layer %d: all layers of a model share one norm style", i);
     }
-  if (e->parallel && !c.final_norm) {
+  for (int i = 0; i < c.num_layers; ++i)
+    if ((e->layers[i].norm_style == MTX_NORM_PRE) != e->prenorm) {
+      delete e;
+      return fail(MTX_ERR_UNSUPPORTED, "layer %d: all layers of a model share one norm style", i);
+    }
+  if ((e->parallel || e->prenorm) && !c.final_norm) {
     delete e;
-    return fail(MTX_ERR_ARG, "a model of parallel layers has a final norm weight");
+    return fail(MTX_ERR_ARG, "a model of parallel or pre-norm layers has a final norm weight");
   }
   if (e->sandwich && c.width > 256 * kSandwichMax) {
     delete e;
@@ -1425,6 +1811,7 @@ int mtx_layered_bind(mtx_layered* e, void* workspace, size_t workspace_bytes) {
   e->xb = base + L.xb;
   e->lat_q = reinterpret_cast<float*>(base + L.lat_q);
   e->lat_o = base + L.lat_o;
+  e->rec_gate = reinterpret_cast<float*>(base + L.rec_gate);
   e->bound = true;
   return MTX_OK;
 }
@@ -1435,7 +1822,7 @@ int mtx_layered_step(mtx_layered* e, const mtx_ragged_batch* b, mtx_stream strea
   if (b->n_want < 0 || b->n_want > e->cfg.max_want) return fail(MTX_ERR_ARG, "n_want = %d outside [0, %d]", b->n_want, e->cfg.max_want);
   if (!b->token || !b->group || !b->pos || !b->page_map || (b->n_want > 0 && (!b->want_rows || !b->logits))) return fail(MTX_ERR_ARG, "null batch array");
   if (b->n_tiles < 0 || b->n_tiles > b->rows) return fail(MTX_ERR_ARG, "n_tiles = %d for %d rows", b->n_tiles, b->rows);
-  if ((e->sandwich || e->parallel) && (b->n_tiles < 1 || !b->tile_row0 || b->n_runs < 1 || b->n_runs > b->rows || !b->run_row0))
+  if ((e->sandwich || e->parallel || e->prenorm) && (b->n_tiles < 1 || !b->tile_row0 || b->n_runs < 1 || b->n_runs > b->rows || !b->run_row0))
     return fail(MTX_ERR_ARG, "this model needs the batch's query tiles and runs");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   return e->cfg.float32 ? step_typed<float>(e, *b, st) : step_typed<bf16>(e, *b, st);

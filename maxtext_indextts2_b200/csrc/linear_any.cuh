@@ -10,7 +10,8 @@
 // Epilogues: LIN_PLAIN  out = acc                      (fp32)
 //            LIN_BIAS   out = acc + bias[col]          (fp32)
 //            LIN_GATED  act[r, f] = gelu_tanh(acc[r, 2f]) * acc[r, 2f + 1]   (the weight rows are interleaved gate / up)
-//            LIN_GATED_CLAMP  act[r, f] = g sigmoid(1.702 g) (u + 1), g = min(acc[r, 2f], limit), u = clamp(acc[r, 2f + 1], -limit, limit)
+//            LIN_GATED_CLAMP  act[r, f] = g sigmoid(1.702 g) (u + 1), g = min(acc[r, 2f], limit), u = clamp(acc[r, 2f + 1], -limit, limit);
+//                             limit <= 0: act[r, f] = silu(acc[r, 2f]) * acc[r, 2f + 1], no limits
 //            LIN_ACT    act[r, c] = acc                  (in the matmul dtype, row pitch ldo: the input of another product)
 //            LIN_RELU2  act[r, c] = max(acc, 0)^2
 //
@@ -75,6 +76,9 @@ __device__ __forceinline__ float clamped_gate_f(float g, float u, float limit) {
   return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
 }
 
+// silu(g) * u
+__device__ __forceinline__ float silu_gate_f(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+
 __device__ __forceinline__ float gelu_tanh_f(float z) {
   const float c = 0.7978845608028654f;  // sqrt(2 / pi)
   return 0.5f * z * (1.0f + tanhf(c * (z + 0.044715f * z * z * z)));
@@ -99,7 +103,7 @@ __device__ __forceinline__ void lin_store_pair(const LinArgs<T>& p, int r, int c
     return;
   }
   if (EPI == LIN_GATED_CLAMP) {
-    p.act[size_t(r) * p.ldo + (c >> 1)] = to_act<T>(clamped_gate_f(v0, v1, p.limit));
+    p.act[size_t(r) * p.ldo + (c >> 1)] = to_act<T>(p.limit > 0.0f ? clamped_gate_f(v0, v1, p.limit) : silu_gate_f(v0, v1));
     return;
   }
   if (EPI == LIN_ACT || EPI == LIN_RELU2) {

@@ -1,8 +1,9 @@
 // Routing of a mixture of experts for a ragged batch (the experts' matrix products are the grouped mode of linear_any.cuh).
 //
-//   moe_route_kernel    per row: s = sigmoid(logits); choice = s + correction; the experts of all but the keep_groups best groups
+//   moe_route_kernel    per row: s = sigmoid(logits) (or, softmax set, the softmax over all experts); choice = s + correction; the experts of all but the keep_groups best groups
 //                       (a group's score = the sum of its two largest choice scores) are barred; the `top` largest remaining choice
-//                       scores are chosen (the lower index wins a tie); weights = s of the chosen / (their sum + 1e-20).  fp32.
+//                       scores are chosen (the lower index wins a tie); weights = s of the chosen / (their sum + 1e-20), or, plain set, s of the
+//                       chosen as it is.  fp32.
 //   moe_sort_kernel     one CTA: counts the (row, choice) entries per expert, lays the experts' slot ranges side by side
 //                       (group_off), gives every entry a slot in its expert's range and records the row each slot reads.
 //   moe_combine_kernel  y[row] (+)= sum over the row's choices, in the order of the choices, of weight * expert output of its slot.
@@ -19,6 +20,8 @@ struct MoeRouteArgs {
   int* chosen;              // [rows, top]
   float* weight;            // [rows, top]
   int experts, top, groups, keep;
+  int softmax;              // 1: s = softmax(logits) over all experts
+  int plain;                // 1: weights = s of the chosen, not renormalised
 };
 
 // one warp per row; shared memory: 2 * experts + groups floats
@@ -29,8 +32,18 @@ __global__ void __launch_bounds__(32) moe_route_kernel(const MoeRouteArgs a) {
   float* gs = c + a.experts;      // [groups]
   griddep_wait();
   const int r = blockIdx.x, lane = threadIdx.x, E = a.experts, per = E / a.groups;
+  float zmax = -INFINITY, zsum = 1.0f;
+  if (a.softmax) {
+    for (int e = lane; e < E; e += 32) zmax = fmaxf(zmax, a.logits[size_t(r) * E + e]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) zmax = fmaxf(zmax, __shfl_xor_sync(0xffffffffu, zmax, o));
+    zsum = 0.0f;
+    for (int e = lane; e < E; e += 32) zsum += expf(a.logits[size_t(r) * E + e] - zmax);
+    zsum = warp_sum(zsum);
+  }
   for (int e = lane; e < E; e += 32) {
-    const float v = 1.0f / (1.0f + expf(-a.logits[size_t(r) * E + e]));
+    const float z = a.logits[size_t(r) * E + e];
+    const float v = a.softmax ? expf(z - zmax) / zsum : 1.0f / (1.0f + expf(-z));
     s[e] = v;
     c[e] = v + (a.correction ? a.correction[e] : 0.0f);
   }
@@ -84,7 +97,7 @@ __global__ void __launch_bounds__(32) moe_route_kernel(const MoeRouteArgs a) {
     }
     __syncwarp();
   }
-  for (int k = lane; k < a.top; k += 32) a.weight[size_t(r) * a.top + k] = s[a.chosen[size_t(r) * a.top + k]] / (total + 1e-20f);
+  for (int k = lane; k < a.top; k += 32) a.weight[size_t(r) * a.top + k] = s[a.chosen[size_t(r) * a.top + k]] / (a.plain ? 1.0f : total + 1e-20f);
 }
 
 // shared memory: (2 * experts + 1) ints

@@ -7,6 +7,9 @@
 //          o = S^T q / (max(|n . q|, e^(-m')) + denom_eps)          (m starts at 0; i, f are log gates)
 //   delta  S <- diag(w) S' - (a u)(u^T S') + k v^T,  o = S^T q    (S' the old state in both first terms)
 //          u = k / sqrt(|k|^2 + key_eps); w = exp(-rate sigmoid(z)), z = up tanh(down x) + bias; a = sigmoid(. + bias), per key channel
+//   gated delta  S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q   (the read-out sees the token's own write)
+//          q, k, v after a short causal convolution over time and silu; q, k unit vectors (q / k heads may serve several heads);
+//          g = exp(-exp(a_log) softplus(z + bias)) per head or per key channel; beta = sigmoid(.)
 //
 // A run (consecutive rows of one sequence) is walked in order from the group's state; a run that starts at position 0 starts
 // from zero instead, so a slot that is handed to another sequence needs no clearing.  Every value column of S is independent of
@@ -16,6 +19,7 @@
 //
 //   recurrent_prepare_kernel   per row: the GLA's decays (low-rank up-projection, bias, sigmoid^(1/tau)) or the mLSTM's two log gates
 //   delta_prepare_kernel       per row: the delta rule's decays, unit keys and removal vectors a u
+//   gdelta_prepare_kernel      per row: the gated delta rule's convolutions, silu, unit vectors, decays and write strengths
 //   recurrent_scan_kernel      the walk
 //   recurrent_out_kernel<T>    per row and head: o / rms(o) * weight * gate(g) * out_scale -> the activation of the output projection
 #pragma once
@@ -26,7 +30,7 @@
 
 namespace mtx {
 
-enum { REC_GLA = 1, REC_MLSTM = 2, REC_DELTA = 3 };
+enum { REC_GLA = 1, REC_MLSTM = 2, REC_DELTA = 3, REC_GDELTA = 4 };
 
 __device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.0f) - log1pf(expf(-fabsf(z))); }
 
@@ -107,6 +111,108 @@ __global__ void __launch_bounds__(256) delta_prepare_kernel(const DeltaPrepareAr
   }
 }
 
+// columns of the plane gdelta_prepare_kernel writes, each part starting on a multiple of four floats
+struct GDeltaCols {
+  int q, k, v, decay, beta, n;
+};
+__host__ __device__ inline GDeltaCols gdelta_cols(int heads, int kv_heads, int dim, int vdim) {
+  GDeltaCols c;
+  auto up4 = [](int x) { return (x + 3) / 4 * 4; };
+  c.q = 0;
+  c.k = up4(kv_heads * dim);
+  c.v = c.k + up4(kv_heads * dim);
+  c.decay = c.v + up4(heads * vdim);
+  c.beta = c.decay + up4(heads * dim);
+  c.n = c.beta + up4(heads);
+  return c;
+}
+
+template <typename T>
+struct GDeltaPrepareArgs {
+  const float* proj;     // [rows, ld]: q | k | v (C = 2 * kv_heads * dim + heads * vdim columns from column 0), then beta at b_col (heads),
+  long long ld;          // the decay's input at a_col (heads, or rank), the low-rank gate's input at g_col (gate_rank)
+  int b_col, a_col, g_col;
+  int heads, kv_heads, dim, vdim, taps, rank, gate_rank;
+  float key_eps;
+  const float* conv_w;   // [taps, C]
+  const float* state;    // [slots, taps - 1, C]: the projection row of position p at p % (taps - 1)
+  const float* a_log;    // [heads]
+  const float* bias;     // rank == 0: [heads]; else [heads * dim]
+  const float* up_t;     // [rank, heads * dim] (rank > 0)
+  const int* group;
+  const int* pos;
+  float* out;            // [rows, gdelta_cols().n]
+  T* gate_low;           // [rows, gate_rank] the low-rank gate's input in the matmul dtype (gate_rank > 0)
+};
+
+__device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.0f) + log1pf(expf(-fabsf(z))); }
+
+// one CTA per row; dynamic shared memory: C + rank floats.  The row `back` steps before row r is row r - back of the batch when that
+// is the same sequence's previous position, a row of the state when the run began later, and zero before the sequence's start.
+template <typename T>
+__global__ void __launch_bounds__(256) gdelta_prepare_kernel(const GDeltaPrepareArgs<T> a) {
+  extern __shared__ float s_gd[];
+  constexpr int kMaxBack = 16;
+  __shared__ const float* s_src[kMaxBack];
+  griddep_wait();
+  const int r = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
+  const int H = a.heads, G = a.kv_heads, d = a.dim, dv = a.vdim, C = 2 * G * d + H * dv, ring = a.taps - 1;
+  float* buf = s_gd;        // [C] silu(conv(.))
+  float* low = s_gd + C;    // [rank]
+  const int p = a.pos[r], grp = a.group[r];
+  const int n_back = ring < p ? ring : p;
+  const float* row = a.proj + size_t(r) * a.ld;
+  if (tid < n_back && tid < kMaxBack) {
+    const int back = tid + 1, rr = r - back;
+    const bool in_batch = rr >= 0 && a.group[rr] == grp && a.pos[rr] == p - back;
+    s_src[tid] = in_batch ? a.proj + size_t(rr) * a.ld : a.state + (size_t(grp) * ring + (p - back) % ring) * C;
+  }
+  for (int e = tid; e < a.rank; e += blockDim.x) low[e] = row[a.a_col + e];
+  __syncthreads();
+  for (int c = tid; c < C; c += blockDim.x) {
+    float y = row[c] * a.conv_w[size_t(ring) * C + c];
+    for (int back = 1; back <= n_back; ++back) {
+      const float* src;
+      if (back <= kMaxBack) {
+        src = s_src[back - 1];
+      } else {
+        const int rr = r - back;
+        const bool in_batch = rr >= 0 && a.group[rr] == grp && a.pos[rr] == p - back;
+        src = in_batch ? a.proj + size_t(rr) * a.ld : a.state + (size_t(grp) * ring + (p - back) % ring) * C;
+      }
+      y = fmaf(src[c], a.conv_w[size_t(ring - back) * C + c], y);
+    }
+    buf[c] = y / (1.0f + expf(-y));
+  }
+  __syncthreads();
+  const GDeltaCols cc = gdelta_cols(H, G, d, dv);
+  float* out = a.out + size_t(r) * cc.n;
+  for (int u = warp; u < 2 * G; u += nw) {  // unit vectors: the q heads, then the k heads
+    const float* src = buf + u * d;
+    float ss = 0.0f;
+    for (int c = lane; c < d; c += 32) ss = fmaf(src[c], src[c], ss);
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss + a.key_eps);
+    float* dst = out + (u < G ? cc.q + u * d : cc.k + (u - G) * d);
+    for (int c = lane; c < d; c += 32) dst[c] = src[c] * inv;
+  }
+  for (int c = tid; c < H * dv; c += blockDim.x) out[cc.v + c] = buf[2 * G * d + c];
+  for (int c = tid; c < H * d; c += blockDim.x) {
+    const int h = c / d;
+    float z;
+    if (a.rank > 0) {
+      z = a.bias[c];
+      for (int e = 0; e < a.rank; ++e) z = fmaf(a.up_t[size_t(e) * H * d + c], low[e], z);
+    } else {
+      z = row[a.a_col + h] + a.bias[h];
+    }
+    out[cc.decay + c] = expf(-expf(a.a_log[h]) * softplus_f(z));
+  }
+  for (int h = tid; h < H; h += blockDim.x) out[cc.beta + h] = 1.0f / (1.0f + expf(-row[a.b_col + h]));
+  if (a.gate_low)
+    for (int e = tid; e < a.gate_rank; e += blockDim.x) a.gate_low[size_t(r) * a.gate_rank + e] = to_act<T>(row[a.g_col + e]);
+}
+
 struct RecScanArgs {
   const float* proj;   // [rows, ld]: q at q_col, k at k_col, v at v_col (heads x dim, heads x dim, heads x vdim)
   long long ld;
@@ -122,6 +228,10 @@ struct RecScanArgs {
   int heads, dim, vdim, chunk;
   int vec4;            // 1: every staged row starts on a 16-byte boundary and holds whole float4s (set by the host from the sizes)
   float q_scale, denom_eps;
+  // REC_GDELTA: q / k head of head h is h / qk_rep (0 or 1: its own); the decays are the columns [dec_col + h * dim, ..) and the write
+  // strength the column beta_col + h of the plane `aux` with row pitch aux_ld
+  int qk_rep, dec_col, beta_col;
+  long long aux_ld;
 };
 
 // A CTA owns CB value columns of one (run, head): thread (column jl, slice sl) keeps RPT key channels of its column of S in
@@ -175,6 +285,7 @@ __global__ void __launch_bounds__(CB * SL) recurrent_scan_kernel(const RecScanAr
   const bool col_ok = j < dv;
   const int slot = a.group[r0];
   const bool fresh = a.pos[r0] == 0;
+  const int hq = a.qk_rep > 1 ? h / a.qk_rep : h;  // the head whose q and k this head reads
   auto channel = [&](int i) { return (i >> 2) * GS + sl * 4 + (i & 3); };  // this thread's i-th key channel
   const bool vec = (d & 3) == 0;  // whole float4s of the state
   float S[RPT], N[RPT];
@@ -226,9 +337,10 @@ __global__ void __launch_bounds__(CB * SL) recurrent_scan_kernel(const RecScanAr
         float* dst = base + t * TF + r;
         const float* row = a.proj + size_t(r0 + t0 + t) * a.ld;
         if (t0 + t < nr && r < d) {
-          rec_cp_async_16(dst, row + a.q_col + h * d + r);
-          rec_cp_async_16(dst + QP, row + a.k_col + h * d + r);
+          rec_cp_async_16(dst, row + a.q_col + hq * d + r);
+          rec_cp_async_16(dst + QP, row + a.k_col + hq * d + r);
           if (KIND == REC_GLA) rec_cp_async_16(dst + 2 * QP, a.aux + size_t(r0 + t0 + t) * H * d + h * d + r);
+          if (KIND == REC_GDELTA) rec_cp_async_16(dst + 2 * QP, a.aux + size_t(r0 + t0 + t) * a.aux_ld + a.dec_col + h * d + r);
           if (KIND == REC_DELTA) {
             const float* ax = a.aux + size_t(r0 + t0 + t) * 3 * H * d + h * d + r;
             rec_cp_async_16(dst + 2 * QP, ax);
@@ -238,7 +350,7 @@ __global__ void __launch_bounds__(CB * SL) recurrent_scan_kernel(const RecScanAr
         } else {
           *reinterpret_cast<float4*>(dst) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
           *reinterpret_cast<float4*>(dst + QP) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-          if (KIND == REC_GLA || KIND == REC_DELTA) *reinterpret_cast<float4*>(dst + 2 * QP) = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+          if (KIND == REC_GLA || KIND == REC_DELTA || KIND == REC_GDELTA) *reinterpret_cast<float4*>(dst + 2 * QP) = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
           if (KIND == REC_DELTA) {
             *reinterpret_cast<float4*>(dst + 3 * QP) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             *reinterpret_cast<float4*>(dst + 4 * QP) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
@@ -258,9 +370,10 @@ __global__ void __launch_bounds__(CB * SL) recurrent_scan_kernel(const RecScanAr
       const bool ok = t0 + t < nr && r < d;
       const float* row = a.proj + size_t(r0 + t0 + t) * a.ld;
       if (ok) {
-        rec_cp_async_4(dst, row + a.q_col + h * d + r);
-        rec_cp_async_4(dst + QP, row + a.k_col + h * d + r);
+        rec_cp_async_4(dst, row + a.q_col + hq * d + r);
+        rec_cp_async_4(dst + QP, row + a.k_col + hq * d + r);
         if (KIND == REC_GLA) rec_cp_async_4(dst + 2 * QP, a.aux + size_t(r0 + t0 + t) * H * d + h * d + r);
+        if (KIND == REC_GDELTA) rec_cp_async_4(dst + 2 * QP, a.aux + size_t(r0 + t0 + t) * a.aux_ld + a.dec_col + h * d + r);
         if (KIND == REC_DELTA) {
           const float* ax = a.aux + size_t(r0 + t0 + t) * 3 * H * d + h * d + r;
           rec_cp_async_4(dst + 2 * QP, ax);
@@ -270,7 +383,7 @@ __global__ void __launch_bounds__(CB * SL) recurrent_scan_kernel(const RecScanAr
       } else {
         dst[0] = 0.0f;
         dst[QP] = 0.0f;
-        if (KIND == REC_GLA || KIND == REC_DELTA) dst[2 * QP] = 1.0f;
+        if (KIND == REC_GLA || KIND == REC_DELTA || KIND == REC_GDELTA) dst[2 * QP] = 1.0f;
         if (KIND == REC_DELTA) dst[3 * QP] = dst[4 * QP] = 0.0f;
       }
     }
@@ -287,6 +400,13 @@ __global__ void __launch_bounds__(CB * SL) recurrent_scan_kernel(const RecScanAr
         float* dst = base + t * TF + 3 * QP + CB + w;
         if (t0 + t < nr) rec_cp_async_4(dst, a.aux + size_t(r0 + t0 + t) * 2 * H + w * H + h);
         else dst[0] = w ? 0.0f : -INFINITY;  // (forget gate 0, input gate -inf: keep = 1, put = 0)
+      }
+    }
+    if (KIND == REC_GDELTA) {  // the write strength beta (0 beyond the run: nothing is written)
+      for (int t = tid; t < TL; t += NT) {
+        float* dst = base + t * TF + 3 * QP + CB;
+        if (t0 + t < nr) rec_cp_async_4(dst, a.aux + size_t(r0 + t0 + t) * a.aux_ld + a.beta_col + h);
+        else dst[0] = 0.0f;
       }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
@@ -341,6 +461,38 @@ __global__ void __launch_bounds__(CB * SL) recurrent_scan_kernel(const RecScanAr
             S[i4 + 1] = fmaf(a4.y, S[i4 + 1], k4.y * v);
             S[i4 + 2] = fmaf(a4.z, S[i4 + 2], k4.z * v);
             S[i4 + 3] = fmaf(a4.w, S[i4 + 3], k4.w * v);
+            part[u] = fmaf(S[i4], q4.x, part[u]);
+            part[u] = fmaf(S[i4 + 1], q4.y, part[u]);
+            part[u] = fmaf(S[i4 + 2], q4.z, part[u]);
+            part[u] = fmaf(S[i4 + 3], q4.w, part[u]);
+          }
+        } else if (KIND == REC_GDELTA) {
+          // the column decays; what it then holds along k, added over the column's slices, is taken off the written value
+          const float* al = k + QP;
+          const float beta = tok[3 * QP + CB];
+          float along = 0.0f;
+#pragma unroll
+          for (int i4 = 0; i4 < RPT; i4 += 4) {
+            const float4 k4 = *reinterpret_cast<const float4*>(k + i4 * SL), a4 = *reinterpret_cast<const float4*>(al + i4 * SL);
+            S[i4] *= a4.x;
+            S[i4 + 1] *= a4.y;
+            S[i4 + 2] *= a4.z;
+            S[i4 + 3] *= a4.w;
+            along = fmaf(S[i4], k4.x, along);
+            along = fmaf(S[i4 + 1], k4.y, along);
+            along = fmaf(S[i4 + 2], k4.z, along);
+            along = fmaf(S[i4 + 3], k4.w, along);
+          }
+#pragma unroll
+          for (int o = 1; o < SL; o <<= 1) along += __shfl_xor_sync(0xffffffffu, along, o);
+          const float w = beta * (v - along);
+#pragma unroll
+          for (int i4 = 0; i4 < RPT; i4 += 4) {
+            const float4 k4 = *reinterpret_cast<const float4*>(k + i4 * SL), q4 = *reinterpret_cast<const float4*>(q + i4 * SL);
+            S[i4] = fmaf(k4.x, w, S[i4]);
+            S[i4 + 1] = fmaf(k4.y, w, S[i4 + 1]);
+            S[i4 + 2] = fmaf(k4.z, w, S[i4 + 2]);
+            S[i4 + 3] = fmaf(k4.w, w, S[i4 + 3]);
             part[u] = fmaf(S[i4], q4.x, part[u]);
             part[u] = fmaf(S[i4 + 1], q4.y, part[u]);
             part[u] = fmaf(S[i4 + 2], q4.z, part[u]);

@@ -14,10 +14,15 @@
 // Optional parts, each off when its pointer is null: a distance penalty slopes[h] * (i - j) taken off the scaled score; a sink
 // (exp(sink[h]) in the denominator, with no key and no value); a gate sigmoid(gate[row, h]) on head h's output; RMS norms of the
 // query and key heads before the rotation; the rotation's other pairing (i, i + rot_dims / 2); keys and values taken from the
-// pools of an earlier layer (the layer then appends nothing).
+// pools of an earlier layer (the layer then appends nothing); RMS norms over the whole query / key projection instead of head by
+// head; a cap on the scaled score, cap * tanh(s / cap); and pooled blocks: beside the window's tokens a query at i sees one mean
+// key / value per block of `pool` tokens that ends at or before i - window (block b = positions b pool .. b pool + pool - 1), in
+// the same softmax.  The means live in pools of their own with pool_slots blocks per page, on the sequence's page map (block b in
+// page b / pool_slots), and the kernels walk them as a first segment of keys before the window's tokens.
 //
 //   rope_append_kernel         per row: bias already in the projection; rotates q and k, writes q, appends k and v to the pages
 //   qk_prepare_append_kernel   the same with the optional head norms, either pairing, and layers that append nothing
+//   pool_append_kernel         per row that completes a block: the means of the block's cached keys and values into the pooled pools
 //   softmax_attention_rows_kernel<T>   one CTA per (query tile of <= 16 rows of one sequence, query head); keys walked in tiles
 //                              staged as fp32 in shared memory; running maximum and sum per row; everything fp32 (T is only the
 //                              dtype of q, the pools and the output).  Serves float32 engines, every geometry, and decode rows.
@@ -119,6 +124,7 @@ struct QkPrepareArgs {
   int heads, kv_heads, dim, vdim, rot_dims, rot_half, shared_kv;
   int num_pages, tokens_per_page, max_pages;
   float eps;
+  int norm_whole;        // 1: q_norm [H * d] / k_norm [G * d]: the whole projection is brought to unit RMS at once
 };
 
 // angle of channel pair c at position p, reduced to [-pi, pi] in double before the fp32 sine and cosine
@@ -137,12 +143,27 @@ __global__ void __launch_bounds__(256) qk_prepare_append_kernel(const QkPrepareA
   const int p = a.pos[r], grp = a.group[r];
   const size_t slot = size_t(a.page_map[size_t(grp) * a.max_pages + p / a.tokens_per_page]) * a.tokens_per_page + p % a.tokens_per_page;
   const double dp = double(p);
+  float inv_all[2] = {1.0f, 1.0f};  // norm_whole: of the query / the key projection
+  if (a.norm_whole) {
+    __shared__ float red[8];
+    for (int which = 0; which < 2; ++which) {
+      const int n = which == 0 ? H * d : G * d;
+      if (n == 0 || !(which == 0 ? a.q_norm : a.k_norm)) continue;
+      const float* src = row + (which == 0 ? a.q_col : a.k_col);
+      float ss = 0.0f;
+      for (int c = tid; c < n; c += blockDim.x) ss = fmaf(src[c], src[c], ss);
+      inv_all[which] = 1.0f / sqrtf(block_sum(ss, red) / float(n) + a.eps);
+    }
+  }
   for (int u = warp; u < H + G; u += nw) {
     const bool is_q = u < H;
     const float* src = row + (is_q ? a.q_col + u * d : a.k_col + (u - H) * d);
     const float* w = is_q ? a.q_norm : a.k_norm;
     float inv = 1.0f;
-    if (w) {
+    if (w && a.norm_whole) {
+      inv = inv_all[is_q ? 0 : 1];
+      w += (is_q ? u : u - H) * d;
+    } else if (w) {
       float ss = 0.0f;
       for (int c = lane; c < d; c += 32) ss = fmaf(src[c], src[c], ss);
       ss = warp_sum(ss);
@@ -164,6 +185,44 @@ __global__ void __launch_bounds__(256) qk_prepare_append_kernel(const QkPrepareA
   for (int e = tid; e < G * dv; e += blockDim.x) {
     const int kv = e / dv, c = e % dv;
     a.v_pages[(size_t(kv) * a.num_pages * a.tokens_per_page + slot) * dv + c] = to_act<T>(row[a.v_col + e]);
+  }
+}
+
+template <typename T>
+struct PoolAppendArgs {
+  const T* k_pages;
+  const T* v_pages;
+  T* kp_pages;  // [G, num_pages, pool_slots, d]
+  T* vp_pages;  // [G, num_pages, pool_slots, dv]
+  const int* group;
+  const int* pos;
+  const int* page_map;
+  int kv_heads, dim, vdim, pool, pool_slots;
+  int num_pages, tokens_per_page, max_pages;
+};
+
+// one CTA per row; the row whose position ends a block of `pool` tokens adds the block's cached keys and values up in order of
+// position (fp32) and writes their means; every other CTA leaves at once
+template <typename T>
+__global__ void __launch_bounds__(256) pool_append_kernel(const PoolAppendArgs<T> a) {
+  griddep_wait();
+  const int r = blockIdx.x, p = a.pos[r], P = a.pool;
+  if ((p + 1) % P != 0) return;
+  const int b = p / P, d = a.dim, dv = a.vdim, G = a.kv_heads, tpp = a.tokens_per_page;
+  const int* pages = a.page_map + size_t(a.group[r]) * a.max_pages;
+  const size_t dst = size_t(pages[b / a.pool_slots]) * a.pool_slots + b % a.pool_slots;
+  const float inv = 1.0f / float(P);
+  for (int e = threadIdx.x; e < G * (d + dv); e += blockDim.x) {
+    const bool is_k = e < G * d;
+    const int f = is_k ? e : e - G * d, w = is_k ? d : dv, kv = f / w, c = f % w;
+    const T* src = is_k ? a.k_pages : a.v_pages;
+    float acc = 0.0f;
+    for (int j = b * P; j <= p; ++j) {
+      const size_t row = size_t(kv) * a.num_pages * tpp + size_t(pages[j / tpp]) * tpp + j % tpp;
+      acc += act_f32(src[row * w + c]);
+    }
+    T* out = is_k ? a.kp_pages : a.vp_pages;
+    out[(size_t(kv) * a.num_pages * a.pool_slots + dst) * w + c] = to_act<T>(acc * inv);
   }
 }
 
@@ -191,7 +250,22 @@ struct SoftmaxAttnArgs {
   const float* sink;    // [H]: exp(sink[h]) joins the denominator (it enters the first key split's running maximum and sum)
   const float* gate;    // [rows, ld_gate]: head h's output is multiplied by sigmoid(gate[row, h])
   long long ld_gate;
+  float softcap;        // > 0: the scaled score becomes softcap * tanh(score / softcap)
+  int pool, pool_slots; // pool > 0: pooled blocks (see the head of this file); needs window > 0
+  const T* kp_pages;    // [G, num_pages, pool_slots, d]
+  const T* vp_pages;    // [G, num_pages, pool_slots, dv]
 };
+
+// blocks of `pool` tokens that the query at position i sees: those that end at or before i - window
+__device__ __forceinline__ int smax_blocks_seen(int i, int window, int pool) {
+  const int past = i - window + 1;  // tokens before the window
+  return (pool > 0 && past > 0) ? past / pool : 0;
+}
+
+// cap * tanh(s / cap) by one exponential and one division: absolute error of a few 1e-7 * cap
+__device__ __forceinline__ float smax_softcap_fast(float s, float cap) {
+  return cap * (1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * s / cap)));
+}
 
 __device__ __forceinline__ float smax_gate(const float* gate, long long ld, int row, int h) {
   return gate ? 1.0f / (1.0f + expf(-gate[size_t(row) * ld + h])) : 1.0f;
@@ -233,30 +307,39 @@ __global__ void __launch_bounds__(kSmaxThreads) softmax_attention_rows_kernel(co
 #pragma unroll
   for (int u = 0; u < kSmaxMaxAcc; ++u) acc[u] = 0.0f;
   const int* pages = a.page_map + size_t(grp) * a.max_pages;
-  const size_t head_rows = size_t(g) * a.num_pages * a.tokens_per_page;
-  for (int j0 = lo; j0 <= p_last; j0 += kSmaxKeys) {
-    const int nk = p_last - j0 + 1 < kSmaxKeys ? p_last - j0 + 1 : kSmaxKeys;
+  const int nb_last = smax_blocks_seen(p_last, a.window, a.pool);
+  // two segments of keys: the pooled blocks 0 .. nb_last - 1 (if any), then the tokens lo .. p_last
+  for (int seg = nb_last > 0 ? 0 : 1; seg < 2; ++seg) {
+  const bool pooled = seg == 0;
+  const int begin = pooled ? 0 : lo, end = pooled ? nb_last - 1 : p_last, tpp = pooled ? a.pool_slots : a.tokens_per_page;
+  const T* kpool = pooled ? a.kp_pages : a.k_pages;
+  const T* vpool = pooled ? a.vp_pages : a.v_pages;
+  const size_t head_rows = size_t(g) * a.num_pages * tpp;
+  for (int j0 = begin; j0 <= end; j0 += kSmaxKeys) {
+    const int nk = end - j0 + 1 < kSmaxKeys ? end - j0 + 1 : kSmaxKeys;
     __syncthreads();
     for (int e = tid; e < nk * d; e += kSmaxThreads) {
       const int jj = e / d, c = e % d, j = j0 + jj;
-      const size_t row = head_rows + size_t(pages[j / a.tokens_per_page]) * a.tokens_per_page + j % a.tokens_per_page;
-      sk[jj * (d + 1) + c] = act_f32(a.k_pages[row * d + c]);
+      const size_t row = head_rows + size_t(pages[j / tpp]) * tpp + j % tpp;
+      sk[jj * (d + 1) + c] = act_f32(kpool[row * d + c]);
     }
     for (int e = tid; e < nk * dv; e += kSmaxThreads) {
       const int jj = e / dv, c = e % dv, j = j0 + jj;
-      const size_t row = head_rows + size_t(pages[j / a.tokens_per_page]) * a.tokens_per_page + j % a.tokens_per_page;
-      sv[jj * dv + c] = act_f32(a.v_pages[row * dv + c]);
+      const size_t row = head_rows + size_t(pages[j / tpp]) * tpp + j % tpp;
+      sv[jj * dv + c] = act_f32(vpool[row * dv + c]);
     }
     __syncthreads();
     for (int e = tid; e < nr * kSmaxKeys; e += kSmaxThreads) {
       const int i = e / kSmaxKeys, jj = e % kSmaxKeys, j = j0 + jj, pi = p0 + i;
       float s = -INFINITY;
-      if (jj < nk && j <= pi && (a.window <= 0 || pi - j < a.window)) {
+      const bool seen = pooled ? j < smax_blocks_seen(pi, a.window, a.pool) : (j <= pi && (a.window <= 0 || pi - j < a.window));
+      if (jj < nk && seen) {
         const float* qv = sq + i * d;
         const float* kv = sk + jj * (d + 1);
         s = 0.0f;
         for (int c = 0; c < d; ++c) s = fmaf(qv[c], kv[c], s);
-        s -= slope * float(pi - j);
+        if (a.softcap > 0.0f) s = a.softcap * tanhf(s / a.softcap);
+        if (!pooled) s -= slope * float(pi - j);
       }
       sp[e] = s;
     }
@@ -289,6 +372,7 @@ __global__ void __launch_bounds__(kSmaxThreads) softmax_attention_rows_kernel(co
         acc[u] = s;
       }
     }
+  }
   }
   __syncthreads();
 #pragma unroll
@@ -349,29 +433,38 @@ __global__ void __launch_bounds__(128) softmax_attention_mma_kernel(const Softma
   const int* pages = a.page_map + size_t(grp) * a.max_pages;
   const size_t head_rows = size_t(kvh) * a.num_pages * a.tokens_per_page;
   const int page_shift = (a.tokens_per_page & (a.tokens_per_page - 1)) == 0 ? __ffs(a.tokens_per_page) - 1 : -1;  // pages of 2^n tokens: no division per key
-  const int all_key_tiles = (p_last - lo) / KT + 1;
+  // the key tiles: first those of the pooled blocks 0 .. nb_last - 1 (if any), then those of the tokens lo .. p_last
+  const int nb_last = smax_blocks_seen(p_last, a.window, a.pool), pool_tiles = (nb_last + KT - 1) / KT;
+  const int pool_shift = (a.pool_slots & (a.pool_slots - 1)) == 0 && a.pool_slots > 0 ? __ffs(a.pool_slots) - 1 : -1;
+  const size_t pool_head_rows = size_t(kvh) * a.num_pages * a.pool_slots;
+  const int all_key_tiles = pool_tiles + (p_last - lo) / KT + 1;
   int tile_lo = 0, n_key_tiles = all_key_tiles;
   if (a.splits > 1) {
     const int per = (all_key_tiles + a.splits - 1) / a.splits;
     tile_lo = int(blockIdx.z) * per;
     n_key_tiles = all_key_tiles - tile_lo < per ? all_key_tiles - tile_lo : per;
     if (n_key_tiles < 0) n_key_tiles = 0;
-    lo += tile_lo * KT;
   }
 
   const bool same_kv = a.k_pages == a.v_pages;  // the values are the cached keys' rows themselves: one copy of a tile serves both
   auto load_tile = [&](int it, int stage) {
     bf16* sk = stage0 + size_t(stage) * 2 * KT * PITCH;
     bf16* sv = sk + KT * PITCH;
-    const int j0 = lo + it * KT;
+    const int gt = tile_lo + it;
+    const bool pooled = gt < pool_tiles;
+    const int j0 = pooled ? gt * KT : lo + (gt - pool_tiles) * KT, last = pooled ? nb_last - 1 : p_last;
+    const int tpp = pooled ? a.pool_slots : a.tokens_per_page, shift = pooled ? pool_shift : page_shift;
+    const size_t hr = pooled ? pool_head_rows : head_rows;
+    const bf16* kpool = pooled ? a.kp_pages : a.k_pages;
+    const bf16* vpool = pooled ? a.vp_pages : a.v_pages;
     constexpr int CH = D / 8;  // 16-byte chunks per row
     for (int e = tid; e < KT * CH; e += nthreads) {
       const int jj = e / CH, c = e % CH, j = j0 + jj;
-      const bool ok = j <= p_last;
-      const int pg = page_shift >= 0 ? (j >> page_shift) : j / a.tokens_per_page;
-      const size_t row = ok ? head_rows + size_t(pages[pg]) * a.tokens_per_page + (j - pg * a.tokens_per_page) : 0;
-      cp_async_16(sk + jj * PITCH + c * 8, a.k_pages + row * D + c * 8, ok);
-      if (!same_kv) cp_async_16(sv + jj * PITCH + c * 8, a.v_pages + row * D + c * 8, ok);
+      const bool ok = j <= last;
+      const int pg = shift >= 0 ? (j >> shift) : j / tpp;
+      const size_t row = ok ? hr + size_t(pages[pg]) * tpp + (j - pg * tpp) : 0;
+      cp_async_16(sk + jj * PITCH + c * 8, kpool + row * D + c * 8, ok);
+      if (!same_kv) cp_async_16(sv + jj * PITCH + c * 8, vpool + row * D + c * 8, ok);
     }
     cp_async_commit();
   };
@@ -402,6 +495,7 @@ __global__ void __launch_bounds__(128) softmax_attention_mma_kernel(const Softma
   }
   const float slope = a.slopes ? a.slopes[h] : 0.0f;
   const int pi0 = p0 + g, pi1 = p0 + g + 8;
+  const int nb0 = smax_blocks_seen(pi0, a.window, a.pool), nb1 = smax_blocks_seen(pi1, a.window, a.pool);
 
   if (n_key_tiles > 0) load_tile(0, 0);
   for (int it = 0; it < n_key_tiles; ++it) {
@@ -415,7 +509,9 @@ __global__ void __launch_bounds__(128) softmax_attention_mma_kernel(const Softma
     if (active) {
       const bf16* sk = stage0 + size_t(it & 1) * 2 * KT * PITCH;
       const bf16* sv = same_kv ? sk : sk + KT * PITCH;
-      const int j0 = lo + it * KT;
+      const int gt = tile_lo + it;
+      const bool pooled = gt < pool_tiles;
+      const int j0 = pooled ? gt * KT : lo + (gt - pool_tiles) * KT;
       float s[KT / 8][4];
 #pragma unroll
       for (int nb = 0; nb < KT / 8; ++nb) {
@@ -432,8 +528,10 @@ __global__ void __launch_bounds__(128) softmax_attention_mma_kernel(const Softma
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int j = j0 + nb * 8 + 2 * t + (e & 1), pi = (e & 2) ? pi1 : pi0;
-          const bool seen = j <= pi && (a.window <= 0 || pi - j < a.window);
-          s[nb][e] = seen ? s[nb][e] * a.scale - slope * float(pi - j) : -INFINITY;
+          const bool seen = pooled ? j < ((e & 2) ? nb1 : nb0) : (j <= pi && (a.window <= 0 || pi - j < a.window));
+          float sc = s[nb][e] * a.scale;
+          if (a.softcap > 0.0f) sc = smax_softcap_fast(sc, a.softcap);
+          s[nb][e] = seen ? (pooled ? sc : sc - slope * float(pi - j)) : -INFINITY;
         }
         mx0 = fmaxf(mx0, fmaxf(s[nb][0], s[nb][1]));
         mx1 = fmaxf(mx1, fmaxf(s[nb][2], s[nb][3]));
@@ -558,25 +656,34 @@ __global__ void __launch_bounds__(kSdecWarps * 32) softmax_attention_decode_kern
   const int* pages = a.page_map + size_t(grp) * a.max_pages;
   const size_t head_rows = size_t(kvh) * a.num_pages * a.tokens_per_page;
   const int page_shift = (a.tokens_per_page & (a.tokens_per_page - 1)) == 0 ? __ffs(a.tokens_per_page) - 1 : -1;  // pages of 2^n tokens: no division per key
-  const int all_key_tiles = (pos - lo) / KT + 1;
+  // the key tiles: first those of the pooled blocks 0 .. nb - 1 (if any), then those of the tokens lo .. pos
+  const int nb = smax_blocks_seen(pos, a.window, a.pool), pool_tiles = (nb + KT - 1) / KT;
+  const int pool_shift = (a.pool_slots & (a.pool_slots - 1)) == 0 && a.pool_slots > 0 ? __ffs(a.pool_slots) - 1 : -1;
+  const size_t pool_head_rows = size_t(kvh) * a.num_pages * a.pool_slots;
+  const int all_key_tiles = pool_tiles + (pos - lo) / KT + 1;
   const int per = (all_key_tiles + a.splits - 1) / a.splits;
   const int tile_lo = int(blockIdx.z) * per;
   int n_key_tiles = all_key_tiles - tile_lo < per ? all_key_tiles - tile_lo : per;
   if (n_key_tiles < 0) n_key_tiles = 0;
-  const int first = lo + tile_lo * KT;
 
   auto load_tile = [&](int it, int stage) {
     bf16* sk = stage0 + size_t(stage) * stage_elems;
     bf16* sv = sk + KT * PITCH;
-    const int j0 = first + it * KT;
+    const int gt = tile_lo + it;
+    const bool pooled = gt < pool_tiles;
+    const int j0 = pooled ? gt * KT : lo + (gt - pool_tiles) * KT, last = pooled ? nb - 1 : pos;
+    const int tpp = pooled ? a.pool_slots : a.tokens_per_page, shift = pooled ? pool_shift : page_shift;
+    const size_t hr = pooled ? pool_head_rows : head_rows;
+    const bf16* kpool = pooled ? a.kp_pages : a.k_pages;
+    const bf16* vpool = pooled ? a.vp_pages : a.v_pages;
     constexpr int CH = D / 8;
     for (int e = tid; e < KT * CH; e += NT) {
       const int jj = e / CH, c = e % CH, j = j0 + jj;
-      const bool ok = j <= pos;
-      const int pg = page_shift >= 0 ? (j >> page_shift) : j / a.tokens_per_page;
-      const size_t r = ok ? head_rows + size_t(pages[pg]) * a.tokens_per_page + (j - pg * a.tokens_per_page) : 0;
-      cp_async_16(sk + jj * PITCH + c * 8, a.k_pages + r * D + c * 8, ok);
-      if (!same_kv) cp_async_16(sv + jj * PITCH + c * 8, a.v_pages + r * D + c * 8, ok);
+      const bool ok = j <= last;
+      const int pg = shift >= 0 ? (j >> shift) : j / tpp;
+      const size_t r = ok ? hr + size_t(pages[pg]) * tpp + (j - pg * tpp) : 0;
+      cp_async_16(sk + jj * PITCH + c * 8, kpool + r * D + c * 8, ok);
+      if (!same_kv) cp_async_16(sv + jj * PITCH + c * 8, vpool + r * D + c * 8, ok);
     }
     cp_async_commit();
   };
@@ -618,8 +725,10 @@ __global__ void __launch_bounds__(kSdecWarps * 32) softmax_attention_decode_kern
     __syncthreads();
     const bf16* sk = stage0 + size_t(it & 1) * stage_elems;
     const bf16* sv = same_kv ? sk : sk + KT * PITCH;
-    const int j0 = first + it * KT + warp * 16;  // this warp's 16 keys
-    if (j0 <= pos) {
+    const int gt = tile_lo + it;
+    const bool pooled = gt < pool_tiles;
+    const int j0 = (pooled ? gt * KT : lo + (gt - pool_tiles) * KT) + warp * 16;  // this warp's 16 keys
+    if (j0 <= (pooled ? nb - 1 : pos)) {
       float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
       const bf16* k0 = sk + (warp * 16 + g) * PITCH + 2 * t;
 #pragma unroll
@@ -633,11 +742,18 @@ __global__ void __launch_bounds__(kSdecWarps * 32) softmax_attention_decode_kern
       }
       // c[0], c[1]: key j0 + g, heads 2t, 2t + 1;  c[2], c[3]: key j0 + g + 8
       const int ja = j0 + g, jb = j0 + g + 8;
-      const bool sa_ = ja <= pos && (a.window <= 0 || pos - ja < a.window), sb_ = jb <= pos && (a.window <= 0 || pos - jb < a.window);
-      c[0] = sa_ ? c[0] * a.scale - slope0 * float(pos - ja) : -INFINITY;
-      c[1] = sa_ ? c[1] * a.scale - slope1 * float(pos - ja) : -INFINITY;
-      c[2] = sb_ ? c[2] * a.scale - slope0 * float(pos - jb) : -INFINITY;
-      c[3] = sb_ ? c[3] * a.scale - slope1 * float(pos - jb) : -INFINITY;
+      const bool sa_ = pooled ? ja < nb : (ja <= pos && (a.window <= 0 || pos - ja < a.window));
+      const bool sb_ = pooled ? jb < nb : (jb <= pos && (a.window <= 0 || pos - jb < a.window));
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        c[e] *= a.scale;
+        if (a.softcap > 0.0f) c[e] = smax_softcap_fast(c[e], a.softcap);
+      }
+      const float da = pooled ? 0.0f : float(pos - ja), db = pooled ? 0.0f : float(pos - jb);
+      c[0] = sa_ ? c[0] - slope0 * da : -INFINITY;
+      c[1] = sa_ ? c[1] - slope1 * da : -INFINITY;
+      c[2] = sb_ ? c[2] - slope0 * db : -INFINITY;
+      c[3] = sb_ ? c[3] - slope1 * db : -INFINITY;
       float mx0 = fmaxf(c[0], c[2]), mx1 = fmaxf(c[1], c[3]);
 #pragma unroll
       for (int sh = 4; sh < 32; sh <<= 1) {

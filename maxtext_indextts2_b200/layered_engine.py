@@ -28,9 +28,9 @@ from . import params as params_lib
 from .maxengine import ExistingPrefix, MaxEngine, ResultTokens  # noqa: F401  (same result types)
 
 _MIXERS = {"window_sigmoid": _lib.MIXER_WINDOW_SIGMOID, "composite": _lib.MIXER_COMPOSITE}
-_NORMS = {"out_gain": _lib.NORM_OUT_GAIN, "sandwich": _lib.NORM_SANDWICH, "parallel": _lib.NORM_PARALLEL}
+_NORMS = {"out_gain": _lib.NORM_OUT_GAIN, "sandwich": _lib.NORM_SANDWICH, "parallel": _lib.NORM_PARALLEL, "pre": _lib.NORM_PRE}
 _FF_KINDS = {"none": _lib.FF_GELU_GATED, "gelu": _lib.FF_GELU_GATED, "clamped": _lib.FF_CLAMPED_GATED, "moe": _lib.FF_MOE, "relu2": _lib.FF_RELU2}
-_RECURRENCES = {"gla": _lib.REC_GLA, "mlstm": _lib.REC_MLSTM, "delta": _lib.REC_DELTA}
+_RECURRENCES = {"gla": _lib.REC_GLA, "mlstm": _lib.REC_MLSTM, "delta": _lib.REC_DELTA, "gdelta": _lib.REC_GDELTA}
 QUERY_TILE_ROWS = 16  # rows of one query tile of the attention kernels (csrc/window_attention_mma.cuh, csrc/softmax_attention.cuh)
 
 _LAYER_MATS = ("wqkv", "wo", "w_gate_up", "w_down", "w_in")
@@ -39,7 +39,10 @@ _LAYER_VECS = ("bqkv", "q_norm", "k_norm", "dist_bias", "head_bias", "talk", "no
 _ATTN_VECS = ("q_norm", "k_norm", "slopes", "sink")
 _LATENT_MATS = ("w_uq", "w_uk_t", "w_uv")
 _LATENT_VECS = ("q_norm", "kv_norm", "sink")
-_REC_VECS = ("decay_up_t", "decay_bias", "gate_bias", "out_norm")
+_REC_VECS = ("decay_up_t", "decay_bias", "gate_bias", "out_norm", "conv_w", "a_log")
+_REC_MATS = ("w_gate_up",)
+_SIDE_MATS = ("gate", "proj")
+_SIDE_VECS = ("norm",)
 _MOE_MATS = ("w_router", "w_gate_up", "w_down", "shared_gate_up", "shared_down")
 _MOE_VECS = ("correction",)
 
@@ -58,6 +61,10 @@ def design_module(config):
     from . import ginodra
 
     return ginodra
+  if config.decoder_block == "ligidra":
+    from . import ligidra
+
+    return ligidra
   raise ValueError(f"decoder_block={config.decoder_block!r} is not a layered design")
 
 
@@ -102,6 +109,8 @@ class LayeredParams:
     self.logit_softcap = float(plan.get("logit_softcap") or 0.0)
     self.logit_scale = float(plan.get("logit_scale") or 1.0)
     self.norm_groups = int(plan.get("norm_groups") or 0)
+    self.embed_norm = vec(plan.get("embed_norm"))
+    self.side_embed = mat(plan.get("side_embed"))
     self.layers = []
     for lp in plan["layers"]:
       d = pack(lp, _LAYER_MATS, _LAYER_VECS)
@@ -112,7 +121,9 @@ class LayeredParams:
         d["latent"] = pack(d["latent"], _LATENT_MATS, _LATENT_VECS)
         d["latent"]["rot_freq"] = put(d["latent"].get("rot_freq"), torch.float64)
       if d.get("rec"):
-        d["rec"] = pack(d["rec"], (), _REC_VECS)
+        d["rec"] = pack(d["rec"], _REC_MATS, _REC_VECS)
+      if d.get("side"):
+        d["side"] = pack(d["side"], _SIDE_MATS, _SIDE_VECS)
       if d.get("moe"):
         d["moe"] = pack(d["moe"], _MOE_MATS, _MOE_VECS)
       self.layers.append(d)
@@ -206,6 +217,7 @@ class LayeredEngine(MaxEngine):
     pm = self.page_manager
     ct = torch.float32 if lp.float32 else torch.bfloat16
     self._pools = []
+    self._pooled = {}  # layer run -> (pooled keys, pooled values) of attention layers that see pooled blocks
     self._states = []  # per layer run: the recurrent state tensors [state slots, ...] (fp32), or ()
     descs = (_lib.LayerDesc * len(lp.layers))()
     ptr = lambda t: t.data_ptr() if t is not None else None
@@ -254,6 +266,20 @@ class LayeredEngine(MaxEngine):
           d.attn.rot_freq, d.attn.k_pages, d.attn.v_pages = ptr(a["rot_freq"]), kp.data_ptr(), vp.data_ptr()
           for k in _ATTN_VECS:
             setattr(d.attn, k, ptr(a.get(k)))
+          d.attn.softcap, d.attn.norm_whole = float(a.get("softcap") or 0.0), int(a.get("norm_whole", 0))
+          P = int(a.get("pool") or 0)
+          if P:  # one mean key / value per block of P tokens, in pools of their own on the same page map
+            tpp = pm.tokens_per_page
+            slots_pp = tpp // P if tpp % P == 0 else tpp
+            src = a.get("kv_from")
+            if src is not None and int(lp.layers[int(src)]["attn"].get("pool") or 0) == P:  # the layer whose cache is read fills them
+              pk, pv = self._pooled[int(src)]
+              d.attn.pool_shared = 1
+            else:
+              pk = torch.zeros(int(a["kv_heads"]), pm.num_pages, slots_pp, int(a["dim"]), dtype=ct, device=dev)
+              pv = torch.zeros(int(a["kv_heads"]), pm.num_pages, slots_pp, int(a["vdim"]), dtype=ct, device=dev)
+            self._pooled[i] = (pk, pv)
+            d.attn.pool, d.attn.pool_slots, d.attn.kp_pages, d.attn.vp_pages = P, slots_pp, pk.data_ptr(), pv.data_ptr()
         elif lat:
           dl = int(lat["kv_rank"]) + int(lat["rot_dim"])
           kp = torch.zeros(1, pm.num_pages, pm.tokens_per_page, dl, dtype=ct, device=dev)  # [latent | rotated key part] per token
@@ -276,6 +302,13 @@ class LayeredEngine(MaxEngine):
             setattr(d.rec, k, ptr(r.get(k)))
           H, dk, dv = int(r["heads"]), int(r["dim"]), int(r["vdim"])
           f32 = torch.float32
+          if r["kind"] == "gdelta":
+            d.rec.kv_heads, d.rec.conv_taps, d.rec.gate_rank = int(r["kv_heads"]), int(r["conv_taps"]), int(r.get("gate_rank", 0))
+            for k in ("conv_w", "a_log", "w_gate_up"):
+              setattr(d.rec, k, ptr(r.get(k)))
+            if d.rec.conv_taps > 1:  # the ring of a sequence's last projection rows (q | k | v before the convolution), per state slot
+              states += (torch.zeros(slots, d.rec.conv_taps - 1, 2 * int(r["kv_heads"]) * dk + H * dv, dtype=f32, device=dev),)
+              d.rec.conv_state = states[-1].data_ptr()
           rec_states = (torch.zeros(slots, H, dv, dk, dtype=f32, device=dev),)
           d.rec.state_s = rec_states[0].data_ptr()
           if r["kind"] == "mlstm":
@@ -288,12 +321,18 @@ class LayeredEngine(MaxEngine):
           d.moe.limit, d.moe.shared_limit = float(m["limit"]), float(m["shared_limit"])
           for k in ("w_router", "correction", "w_gate_up", "w_down", "shared_gate_up", "shared_down"):
             setattr(d.moe, k, ptr(m.get(k)))
+          for k in ("score_softmax", "plain_weights", "act_silu"):
+            setattr(d.moe, k, int(m.get(k, 0)))
+        sd = l.get("side")
+        if sd:
+          d.side_dim, d.side_col = int(sd["dim"]), int(sd["col"])
+          d.side_gate, d.side_proj, d.side_norm = ptr(sd["gate"]), ptr(sd["proj"]), ptr(sd["norm"])
       for k in ("wo", "w_gate_up", "w_down"):
         setattr(d, k, ptr(l.get(k)))
       self._states.append(states)
     self._needs_runs = any(l["mixer"] == "composite" for l in lp.layers)
     self._pool_tensors = []  # every page pool once (a pool that serves two roles or two layers is one tensor)
-    for pool in self._pools:
+    for pool in list(self._pools) + list(self._pooled.values()):
       for t in pool:
         if not any(t is u for u in self._pool_tensors):
           self._pool_tensors.append(t)
@@ -302,7 +341,8 @@ class LayeredEngine(MaxEngine):
         max_rows=self._max_rows, max_want=self._max_rows, num_groups=slots, num_pages=pm.num_pages,
         tokens_per_page=pm.tokens_per_page, max_pages_per_group=pm.max_pages_per_group, eps=float(cfg.normalization_layer_epsilon),
         embed_scale=lp.embed_scale, final_gain=lp.final_gain, embedding=lp.embedding.data_ptr(), head=lp.head.data_ptr(),
-        final_norm=ptr(lp.final_norm), logit_softcap=lp.logit_softcap, norm_groups=lp.norm_groups, logit_scale=lp.logit_scale)
+        final_norm=ptr(lp.final_norm), logit_softcap=lp.logit_softcap, norm_groups=lp.norm_groups, logit_scale=lp.logit_scale,
+        embed_norm=ptr(lp.embed_norm), side_embed=ptr(lp.side_embed), side_width=int(lp.side_embed.shape[1]) if lp.side_embed is not None else 0)
     _lib.check(self.lib.mtx_layered_create(ctypes.byref(c), descs, ctypes.byref(self._handle)))
     ws = int(self.lib.mtx_layered_workspace_bytes(self._handle))
     self._ws = torch.empty(ws + 1024, dtype=torch.uint8, device=dev)

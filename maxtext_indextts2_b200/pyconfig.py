@@ -36,8 +36,8 @@ _VALID_SAMPLING = ("greedy", "weighted", "nucleus", "topk")
 _VALID_AXIS_ORDER = ("0,1,2,3", "0,2,1,3")
 # Designs whose layers are listed one by one (`layer_specs`) and run on the layered engine (layered_engine.py), keyed by
 # decoder_block; ARCHITECTURES maps the "architecture" of a model folder's config.json to the block.
-LAYERED_BLOCKS = ("kifusun", "gugidra", "ginodra")
-ARCHITECTURES = {"Kifusun": "kifusun", "Gugidra": "gugidra", "Ginodra": "ginodra"}
+LAYERED_BLOCKS = ("kifusun", "gugidra", "ginodra", "ligidra")
+ARCHITECTURES = {"Kifusun": "kifusun", "Gugidra": "gugidra", "Ginodra": "ginodra", "Ligidra": "ligidra"}
 
 
 def _string_to_bool(s: str) -> bool:
@@ -136,6 +136,12 @@ def _validate_layered(keys: dict) -> None:
       raise ValueError("norm_groups must divide the width")
     if int(keys["input_conv_taps"]) < 0:
       raise ValueError("input_conv_taps must not be negative")
+  if keys["decoder_block"] == "ligidra":
+    from . import ligidra
+
+    ligidra.validate_layer_specs(keys["layer_specs"])
+    if int(keys["token_side_dim"]) < 0:
+      raise ValueError("token_side_dim must not be negative")
 
 
 def _validate(keys: dict) -> None:
@@ -304,6 +310,10 @@ def from_model_dict(model: dict, **overrides) -> HyperParameters:
     from . import ginodra
 
     keys = ginodra.config_keys(model)
+  elif block == "ligidra":
+    from . import ligidra
+
+    keys = ligidra.config_keys(model)
   keys.update(decoder_block=block, attention="paged", scan_layers=False, weight_dtype="bfloat16")
   keys.update(overrides)
   if "max_prefill_predict_length" not in overrides:  # any prompt that fits the sequence
