@@ -255,3 +255,92 @@ def forward(model: dict, t: Dict[str, np.ndarray], tokens, hooks=None, return_la
     layers.append(x.copy())
   logits = rms_norm(x, t["final.norm"], eps) @ t["embed"].T
   return (logits, np.stack(layers)) if return_layers else logits
+
+
+# -- random models (tests) -----------------------------------------------------------------------------------------------------
+
+
+def bf16_values(x):
+  """float64 array -> the nearest bfloat16 values (round to nearest even), as float64."""
+  a = np.ascontiguousarray(np.asarray(x, dtype=np.float32))
+  bits = a.view(np.uint32).astype(np.uint64)
+  bits = ((bits + 0x7FFF + ((bits >> 16) & 1)) & 0xFFFF0000).astype(np.uint32)
+  return bits.view(np.float32).astype(np.float64).reshape(np.shape(x))
+
+
+def random_model(model: dict, seed: int = 0, rank: int = 6) -> Dict[str, np.ndarray]:
+  """Random weights by the stored names, already bfloat16 values.  `rank`: the low ranks of channel_delta layers."""
+  g = np.random.Generator(np.random.PCG64(seed))
+  E, V, n = int(model["width"]), int(model["vocab"]), len(model["layers"])
+  sd = int((model.get("token_side") or {}).get("dim") or 0)
+  t: Dict[str, np.ndarray] = {}
+  rn = lambda *shape, std=1.0, mean=0.0: bf16_values(g.normal(mean, std, size=shape))
+  un = lambda *shape, lo=0.0, hi=1.0: bf16_values(g.uniform(lo, hi, size=shape))
+  lin = lambda a, b: rn(a, b, std=1.0 / math.sqrt(b))
+  t["embed"], t["embed.norm"], t["final.norm"] = rn(V, E), rn(E, std=0.2, mean=1.0), rn(E, std=0.2, mean=1.0)
+  if sd:
+    t["side.embed"] = rn(V, n * sd)
+  for i, layer in enumerate(model["layers"]):
+    p, q, m = f"l{i}.", f"l{i}.mix.", layer["mixer"]
+    H, G, d, dv = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
+    t[p + "norm1"], t[p + "shift"] = rn(E, std=0.2, mean=1.0), un(E)
+    if layer["type"] == "attention":
+      t[q + "q"], t[q + "q.norm"], t[q + "sink"], t[q + "o"] = lin(H * d, E), rn(H * d, std=0.3, mean=1.5), rn(H, std=1.0), lin(E, H * dv)
+      if m.get("kv_from") is None:
+        t[q + "k"], t[q + "k.norm"], t[q + "v"] = lin(G * d, E), rn(G * d, std=0.3, mean=1.5), lin(G * dv, E)
+    else:
+      taps = int(m["conv"])
+      t[q + "q"], t[q + "k"], t[q + "v"], t[q + "b"] = lin(G * d, E), lin(G * d, E), lin(H * dv, E), lin(H, E)
+      t[q + "q.conv"], t[q + "k.conv"], t[q + "v.conv"] = rn(G * d, taps, std=0.6), rn(G * d, taps, std=0.6), rn(H * dv, taps, std=0.6)
+      t[q + "A_log"], t[q + "norm"], t[q + "o"] = un(H, lo=-3.0, hi=0.5), rn(dv, std=0.2, mean=1.0), lin(E, H * dv)
+      if layer["type"] == "channel_delta":
+        t[q + "a1"], t[q + "a2"], t[q + "dt_bias"] = lin(rank, E), rn(H * d, rank, std=1.0), rn(H * d, std=1.0)
+        t[q + "g1"], t[q + "g2"] = lin(rank + 1, E), rn(H * dv, rank + 1, std=1.0)
+      else:
+        t[q + "a"], t[q + "dt_bias"], t[q + "g"] = lin(H, E), rn(H, std=1.0), lin(H * dv, E)
+    f = layer.get("mlp")
+    if f:
+      t[p + "norm2"] = rn(E, std=0.2, mean=1.0)
+      names = [f"{p}mlp.e{e}." for e in range(int(f["router"]["experts"]))] + ([p + "mlp.shared."] if f.get("shared") else [])
+      for name in names:
+        F = int(f["shared"]["ff"]) if name.endswith("shared.") else int(f["expert"]["ff"])
+        t[name + "gate"], t[name + "up"], t[name + "down"] = lin(F, E), lin(F, E), lin(E, F)
+      t[p + "mlp.router"] = rn(int(f["router"]["experts"]), E, std=3.0 / math.sqrt(E))
+    if sd:
+      t[p + "side.gate"], t[p + "side.proj"], t[p + "side.norm"] = lin(sd, E), lin(E, sd), rn(E, std=0.1, mean=0.4)
+  return t
+
+
+def closest_router_gap(model: dict, t: Dict[str, np.ndarray], tokens) -> float:
+  """The smallest difference, over all rows and routed layers of a sequence, between the score of the last expert that is chosen
+  and the first that is not: a test whose gap is tiny rests on a close call and should take another seed."""
+  gaps = [1.0]
+  eps = float(model["norm"]["eps"])
+  tokens = np.asarray(tokens)
+  x = rms_norm(t["embed"][tokens], t["embed.norm"], eps)
+  side = model.get("token_side")
+  caches: List[Optional[tuple]] = []
+  for i, l in enumerate(model["layers"]):
+    p, m = f"l{i}.mix.", l["mixer"]
+    h = token_shift(rms_norm(x, t[f"l{i}.norm1"], eps), t[f"l{i}.shift"])
+    if l["type"] == "attention":
+      src = m.get("kv_from")
+      y, kv = attention_mixer(h, t, p, m, eps, None if src is None else caches[int(src)])
+      caches.append(kv if src is None else None)
+    else:
+      y = delta_mixer(h, t, p, m, eps, l["type"] == "channel_delta")
+      caches.append(None)
+    x = x + y
+    f = l.get("mlp")
+    if f:
+      hn = rms_norm(x, t[f"l{i}.norm2"], eps)
+      z = hn @ t[f"l{i}.mlp.router"].T
+      s = np.exp(z - z.max(axis=-1, keepdims=True))
+      s = np.sort(s / s.sum(axis=-1, keepdims=True), axis=-1)[:, ::-1]
+      top = int(f["router"]["top"])
+      if top < s.shape[1]:
+        gaps.append(float((s[:, top - 1] - s[:, top]).min()))
+      x = x + moe_ff(hn, t, f"l{i}.mlp.", f)
+    if side:
+      x = x + side_input(x, tokens, t, i, int(side["dim"]), eps)
+  return min(gaps)
