@@ -66,7 +66,7 @@ def parse_args():
   ap.add_argument("--no-verify", action="store_true", help="skip the oracle check of one step of the timed state")
   ap.add_argument("--prompt-len", type=int, default=4000, help="--mode prefill: prompt tokens (BASELINE configs[3]: 4000 of P = 4096)")
   ap.add_argument("--size", default="all", help="--mode layered: one of the sizes of LAYERED_SIZES, or all")
-  ap.add_argument("--design", default="kifusun", choices=["kifusun", "gugidra", "ginodra"], help="--mode layered: the layered design that is measured beside gemma3")
+  ap.add_argument("--design", default="kifusun", choices=["kifusun", "gugidra", "ginodra", "ligidra"], help="--mode layered: the layered design that is measured beside gemma3")
   ap.add_argument("--mode", default="batch", choices=["batch", "vocab-parallel", "prefill", "layered"],
                   help="batch: request-batch partitioned, no collective (default); vocab-parallel: every GPU decodes the same --batch slots, "
                        "the logits projection is sharded over the GPUs and one NCCL all-gather carries the per-shard candidates")
@@ -614,7 +614,7 @@ def run_layered(args):
   """--mode layered: prefill and decode throughput of a layered design (--design) on the layered engine beside the gemma3 block
   (the closest existing model: softmax attention with rotary positions and grouped key heads, norms before and after every
   sublayer, gated feed-forward) at equal layer sizes, both through MaxEngine.  One JSON line per size."""
-  from maxtext_indextts2_b200 import ginodra, gugidra, kifusun, maxengine, pyconfig
+  from maxtext_indextts2_b200 import ginodra, gugidra, kifusun, ligidra, maxengine, pyconfig
 
   D = args.design  # (the keys of the output line carry the design's name)
   names = list(LAYERED_SIZES) if args.size == "all" else [args.size]
@@ -642,6 +642,20 @@ def run_layered(args):
                 ginodra.attention_layer(H, G, d, window=W, kv_from=1, mlp=ginodra.dense_ff(F)),
                 ginodra.latent_layer(H, d // 2, row // 4, d // 2, z["width"] // 2, row - row // 4, mlp=ginodra.dense_ff(F))][:L]
       model = ginodra.model_dict(z["width"], z["vocab"], layers, groups=2, taps=4)
+    elif D == "ligidra":
+      # Ligidra at the same sizes, one layer of each kind: an attention with gemma3's heads and window that also sees one mean key
+      # per block of 16 tokens before the window, a gated delta rule (gemma3's heads over its key heads, half the key channels), a
+      # second attention that reads the first one's cache, a delta rule with per-channel decays (ranks 64); every layer with a routed
+      # feed-forward of gemma3's active size (16 experts of ff / 8, four per token, a shared expert of ff / 2) and a token input of
+      # width / 8 channels
+      H, G, d, F, W = z["heads"], z["kv_heads"], z["dim"], z["ff"], z["window"]
+      ff = lambda: ligidra.moe_ff(16, 4, F // 8, shared_ff=F // 2)
+      scaling = {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}
+      layers = [ligidra.attention_layer(H, G, d, window=W, pool=16, softcap=50.0, rot_scaling=scaling, mlp=ff()),
+                ligidra.delta_layer(H, G, d // 2, d, taps=4, mlp=ff()),
+                ligidra.attention_layer(H, G, d, window=W, pool=16, softcap=50.0, rot_scaling=scaling, kv_from=0, mlp=ff()),
+                ligidra.delta_layer(H, G, d // 2, d, taps=4, per_channel=True, rank=64, mlp=ff())][:L]
+      model = ligidra.model_dict(z["width"], z["vocab"], layers, side_dim=z["width"] // 8)
     else:
       # Gugidra at the same sizes: attention + mLSTM layers and GLA layers in turn; the attention has gemma3's heads (no window: the
       # design has none), the recurrences half as many key channels per head; dense feed-forwards of gemma3's size in turn with

@@ -456,7 +456,9 @@ typedef struct {
                            a causal convolution over time per channel (conv_taps taps, weights conv_w, the last conv_taps - 1
                            projection rows are state) and silu; q and k are then unit vectors x / sqrt(|x|^2 + key_eps), q times
                            q_scale.  beta = sigmoid(.).  g = exp(-exp(a_log[h]) softplus(z + decay_bias)): decay_rank == 0: one z per
-                           head from a projection row; else per key channel, z = up (down x).  Output gate: gate_rank == 0: heads*vdim
+                           head from a projection row; else per key channel, z = up (down x), where decay_up_t holds, in the matmul
+                           dtype, [heads*dim, 2*decay_rank]: the up-projection twice side by side (the device splits down x into two
+                           parts of the matmul dtype so that the product keeps fp32 accuracy).  Output gate: gate_rank == 0: heads*vdim
                            projection rows; else w_gate_up (gate_rank rows of the projection).  Projection rows: [q: kv_heads*dim |
                            k: kv_heads*dim | v: heads*vdim | beta: heads | decay: heads or decay_rank | gate: heads*vdim or gate_rank] */
 

@@ -57,8 +57,8 @@ struct mtx_layered {
   void *xb = nullptr, *lat_o = nullptr;
   // MTX_NORM_PRE layers (they share h and xb with the parallel ones): the output gate of a recurrence whose gate is low-rank
   bool prenorm = false;
-  int max_rec_gate = 0;
-  float* rec_gate = nullptr;
+  int max_rec_gate = 0, max_rec_z = 0;
+  float *rec_gate = nullptr, *rec_z = nullptr;
 };
 
 namespace {
@@ -68,7 +68,7 @@ size_t elem(const mtx_layered* e) { return e->cfg.float32 ? 4 : 2; }
 struct LWs {
   size_t x, y, qkv, v_shared, xa, q, attn, act, wanted, obf, attn_part, total;
   size_t smax_ml, x0, rec_o, rec_aux, moe_logits, moe_weight, moe_y, moe_chosen, moe_slot, moe_row, moe_off, moe_act;
-  size_t h, xb, lat_q, lat_o, rec_gate;
+  size_t h, xb, lat_q, lat_o, rec_gate, rec_z;
 };
 
 LWs layered_layout(const mtx_layered* e) {
@@ -109,6 +109,7 @@ LWs layered_layout(const mtx_layered* e) {
   L.h = take(e->parallel || e->prenorm ? R * c.width * 4 : 4);
   L.xb = take(e->parallel || e->prenorm ? R * c.width * es : 4);
   L.rec_gate = take(R * size_t(e->max_rec_gate > 0 ? e->max_rec_gate : 1) * 4);
+  L.rec_z = take(R * size_t(e->max_rec_z > 0 ? e->max_rec_z : 1) * 4);
   L.lat_q = take(R * size_t(e->max_lat_q > 0 ? e->max_lat_q : 1) * 4);
   L.lat_o = take(R * size_t(e->max_lat_o > 0 ? e->max_lat_o : 1) * es);
   L.total = off;
@@ -262,7 +263,11 @@ int linear_grouped(const void* a, const int* a_row, const void* w, long long w_s
   p.group_off = group_off;
   p.a_row = a_row;
   p.w_group_stride = w_stride;
-  const dim3 grid((n + 63) / 64, (slots + 63) / 64, groups);
+  // up to 64 groups: their row tiles side by side along y (a CTA finds its group by walking the slot ranges); more: a worst-case
+  // range of y per group
+  const bool packed = groups <= 64;
+  p.groups = packed ? groups : 0;
+  const dim3 grid((n + 63) / 64, packed ? (slots + 63) / 64 + groups : (slots + 63) / 64, packed ? 1 : groups);
   if constexpr (sizeof(T) == 4) return launch(linear_f32_kernel<EPI>, grid, dim3(kLinF32Threads), 0, st, p);
   else return launch(linear_mma_kernel<EPI>, grid, dim3(kLinThreads), 0, st, p);
 }
@@ -835,7 +840,8 @@ int composite_layer(mtx_layered* e, int li, const mtx_ragged_batch& b, cudaStrea
   if (l.ff_kind == MTX_FF_MOE) {
     const mtx_moe_desc& m = l.moe;
     const int entries = rows * m.top;
-    MTX_TRY((linear<T, LIN_PLAIN>(e, xa, m.w_router, nullptr, e->moe_logits, nullptr, rows, m.experts, E, st)));
+    if (m.experts <= 64) MTX_TRY(launch(moe_router_kernel<T>, dim3(rows), dim3(256), 0, st, (const T*)xa, static_cast<const T*>(m.w_router), e->moe_logits, m.experts, E));
+    else MTX_TRY((linear<T, LIN_PLAIN>(e, xa, m.w_router, nullptr, e->moe_logits, nullptr, rows, m.experts, E, st)));
     MoeRouteArgs ra;
     memset(&ra, 0, sizeof(ra));
     ra.logits = e->moe_logits;
@@ -1342,36 +1348,52 @@ int prenorm_layer(mtx_layered* e, int li, const mtx_ragged_batch& b, cudaStream_
     const mtx_recurrent_desc& r = l.rec;
     const int G = r.kv_heads > 0 ? r.kv_heads : r.heads, C = 2 * G * r.dim + r.heads * r.vdim;
     const GDeltaCols gc = gdelta_cols(r.heads, G, r.dim, r.vdim);
+    // the low-rank projections: the gate's input rounded to the matmul dtype, the decay's split into two such parts so that its
+    // up-projection (the matrix written twice along k) keeps fp32 accuracy on the tensor cores
+    T* gate_in = static_cast<T*>(e->act);                                                     // [rows, gate_rank]
+    T* decay_in = gate_in + align_up(size_t(c.max_rows), 256) * size_t(r.gate_rank);          // [rows, 2 * decay_rank]
+    if (r.decay_rank > 0 || r.gate_rank > 0) {
+      const long long total = (long long)rows * (r.decay_rank + r.gate_rank);
+      const int blocks = int((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+      MTX_TRY(launch(lowrank_split_kernel<T>, dim3(blocks), dim3(256), 0, st, (const float*)e->qkv, (long long)n_in, pc.ra, r.decay_rank, pc.rg, r.gate_rank, decay_in,
+                     gate_in, (long long)rows));
+    }
+    if (r.decay_rank > 0)  // (the any-shape kernel: its result is fp32; the tcgen05 projection would round it)
+      MTX_TRY((run_linear<T, LIN_PLAIN>(e, decay_in, r.decay_up_t, nullptr, e->rec_z, nullptr, rows, r.heads * r.dim, 2 * r.decay_rank, st)));
+    if (r.gate_rank > 0)
+      MTX_TRY((linear<T, LIN_PLAIN>(e, gate_in, r.w_gate_up, nullptr, e->rec_gate, nullptr, rows, r.heads * r.vdim, r.gate_rank, st)));
     GDeltaPrepareArgs<T> ga;
     memset(&ga, 0, sizeof(ga));
     ga.proj = e->qkv + pc.rq;
     ga.ld = n_in;
     ga.b_col = pc.rb - pc.rq;
     ga.a_col = pc.ra - pc.rq;
-    ga.g_col = pc.rg - pc.rq;
     ga.heads = r.heads;
     ga.kv_heads = G;
     ga.dim = r.dim;
     ga.vdim = r.vdim;
     ga.taps = r.conv_taps;
     ga.rank = r.decay_rank;
-    ga.gate_rank = r.gate_rank;
     ga.key_eps = r.key_eps;
     ga.conv_w = r.conv_w;
     ga.state = r.conv_state;
     ga.a_log = r.a_log;
     ga.bias = r.decay_bias;
-    ga.up_t = r.decay_up_t;
+    ga.z = e->rec_z;
     ga.group = b.group;
     ga.pos = b.pos;
     ga.out = e->rec_aux;
-    ga.gate_low = r.gate_rank > 0 ? static_cast<T*>(e->act) : nullptr;
-    MTX_TRY(launch(gdelta_prepare_kernel<T>, dim3(rows), dim3(256), sizeof(float) * (C + r.decay_rank), st, ga));
+    {
+      // a warp per unit (q / k / v heads, decays per head, write strengths); few rows: the units of a row over several CTAs
+      const int units = 2 * G + 2 * r.heads + 1;
+      int parts = (4 * e->num_sms + rows - 1) / rows;
+      if (parts > (units + 7) / 8) parts = (units + 7) / 8;
+      if (parts < 1) parts = 1;
+      MTX_TRY(launch(gdelta_prepare_kernel<T>, dim3(rows, parts), dim3(256), 0, st, ga));
+    }
     if (r.conv_taps > 1)
       MTX_TRY(launch(conv_state_update_kernel, dim3(b.n_runs, r.conv_taps - 1), dim3(256), 0, st, (const float*)(e->qkv + pc.rq), r.conv_state, b.run_row0, b.group,
                      b.pos, C, r.conv_taps, (long long)n_in));
-    if (r.gate_rank > 0)
-      MTX_TRY((linear<T, LIN_PLAIN>(e, e->act, r.w_gate_up, nullptr, e->rec_gate, nullptr, rows, r.heads * r.vdim, r.gate_rank, st)));
     RecScanArgs ra;
     memset(&ra, 0, sizeof(ra));
     ra.proj = e->rec_aux;
@@ -1419,7 +1441,8 @@ int prenorm_layer(mtx_layered* e, int li, const mtx_ragged_batch& b, cudaStream_
     MTX_TRY(pre_norm_step<T>(e, e->y, nullptr, nullptr, false, -1, l.norm2, b, st));  // x += mixer; xa = unit(x) * norm2
     const int entries = rows * m.top;
     const float limit = m.act_silu ? 0.0f : m.limit, shared_limit = m.act_silu ? 0.0f : m.shared_limit;
-    MTX_TRY((linear<T, LIN_PLAIN>(e, xa, m.w_router, nullptr, e->moe_logits, nullptr, rows, m.experts, E, st)));
+    if (m.experts <= 64) MTX_TRY(launch(moe_router_kernel<T>, dim3(rows), dim3(256), 0, st, (const T*)xa, static_cast<const T*>(m.w_router), e->moe_logits, m.experts, E));
+    else MTX_TRY((linear<T, LIN_PLAIN>(e, xa, m.w_router, nullptr, e->moe_logits, nullptr, rows, m.experts, E, st)));
     MoeRouteArgs ra;
     memset(&ra, 0, sizeof(ra));
     ra.logits = e->moe_logits;
@@ -1639,18 +1662,13 @@ int check_prenorm(mtx_layered* e, int i) {
       return fail(MTX_ERR_ARG, "layer %d: the recurrence's state, output norm, decay constants or convolution is missing", i);
     if (r.decay_rank < 0 || r.gate_rank < 0 || (r.decay_rank > 0 && !r.decay_up_t) || (r.gate_rank > 0 && !r.w_gate_up))
       return fail(MTX_ERR_ARG, "layer %d: a low-rank decay / gate needs its up-projection", i);
-    const size_t smem = sizeof(float) * size_t(2 * G * r.dim + r.heads * r.vdim + r.decay_rank);
-    if (smem > 200 * 1024) return fail(MTX_ERR_UNSUPPORTED, "layer %d: the recurrence's projections do not fit shared memory", i);
-    if (smem > 48 * 1024) {
-      const cudaError_t e1 = cudaFuncSetAttribute(gdelta_prepare_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-      const cudaError_t e2 = cudaFuncSetAttribute(gdelta_prepare_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-      if (e1 != cudaSuccess || e2 != cudaSuccess) cudaGetLastError();  // (no device: the create call only validates)
-    }
     if (r.heads * r.vdim > e->max_rec_o) e->max_rec_o = r.heads * r.vdim;
     const int aux = gdelta_cols(r.heads, G, r.dim, r.vdim).n;
     if (aux > e->max_rec_aux) e->max_rec_aux = aux;
     if (r.gate_rank > 0 && r.heads * r.vdim > e->max_rec_gate) e->max_rec_gate = r.heads * r.vdim;
-    if (r.gate_rank > e->max_ff) e->max_ff = r.gate_rank;  // (the low-rank gate's input waits in the plane of the feed-forward's activation)
+    if (r.decay_rank > 0 && r.heads * r.dim > e->max_rec_z) e->max_rec_z = r.heads * r.dim;
+    // (the low-rank projections' inputs wait in the plane of the feed-forward's activation)
+    if (r.gate_rank + 2 * r.decay_rank > e->max_ff) e->max_ff = r.gate_rank + 2 * r.decay_rank;
   }
   const PreCols pc = pre_cols(l);
   if (l.n_in < pc.n) return fail(MTX_ERR_ARG, "layer %d: n_in = %d, the mixer needs %d projection rows", i, l.n_in, pc.n);
@@ -1812,6 +1830,7 @@ int mtx_layered_bind(mtx_layered* e, void* workspace, size_t workspace_bytes) {
   e->lat_q = reinterpret_cast<float*>(base + L.lat_q);
   e->lat_o = base + L.lat_o;
   e->rec_gate = reinterpret_cast<float*>(base + L.rec_gate);
+  e->rec_z = reinterpret_cast<float*>(base + L.rec_z);
   e->bound = true;
   return MTX_OK;
 }

@@ -21,7 +21,9 @@
 //
 // Grouped mode (group_off != null; a mixture of experts): blockIdx.z names a group with its own weight matrix; the group's rows are
 // the slots [group_off[g], group_off[g + 1]); slot s reads row a_row[s] of `a` (or row s when a_row is null) and writes row s of the
-// output.  CTAs beyond a group's last row tile leave at once, so the grid is sized for the worst case without a host round trip.
+// output.  CTAs beyond a group's last row tile leave at once, so the grid is sized for the worst case without a host round trip;
+// with `groups` set the grid's y walks the groups' row tiles one group after the other (at most ceil(slots / tile) + groups tiles
+// in all), which leaves few CTAs without work when there are many groups.
 #pragma once
 
 #include "common.cuh"
@@ -44,11 +46,14 @@ struct LinArgs {
   const int* a_row;        // grouped mode: [slots] row of `a` per slot, or null
   long long w_group_stride;  // grouped / batched mode: elements between two groups' weights
   long long batch_a, batch_o;  // batched mode: columns between two batches' inputs / outputs
+  int groups;              // grouped mode, > 0: the grid's y walks the groups' row tiles one group after the other (gridDim.z == 1,
+                           // gridDim.y >= ceil(slots / tile) + groups) instead of every group owning a worst-case range of y
 };
 
 // grouped mode: the argument block of this CTA's group (false: the CTA has no rows)
 template <typename T>
-__device__ __forceinline__ bool lin_enter_group(LinArgs<T>& p, int tile_rows) {
+__device__ __forceinline__ bool lin_enter_group(LinArgs<T>& p, int tile_rows, int& row_tile) {
+  row_tile = blockIdx.y;
   if (p.group_off == nullptr) {
     if (p.batch_a != 0 || p.batch_o != 0) {
       const size_t b = blockIdx.z;
@@ -59,8 +64,19 @@ __device__ __forceinline__ bool lin_enter_group(LinArgs<T>& p, int tile_rows) {
     }
     return true;
   }
-  const int g = blockIdx.z, s0 = p.group_off[g], cnt = p.group_off[g + 1] - s0;
-  if (int(blockIdx.y) * tile_rows >= cnt) return false;
+  int g = blockIdx.z;
+  if (p.groups > 0) {  // whose tile is this?
+    int t = blockIdx.y;
+    for (g = 0; g < p.groups; ++g) {
+      const int nt = (p.group_off[g + 1] - p.group_off[g] + tile_rows - 1) / tile_rows;
+      if (t < nt) break;
+      t -= nt;
+    }
+    if (g == p.groups) return false;
+    row_tile = t;
+  }
+  const int s0 = p.group_off[g], cnt = p.group_off[g + 1] - s0;
+  if (row_tile * tile_rows >= cnt) return false;
   p.rows = cnt;
   p.w += size_t(g) * p.w_group_stride;
   if (p.a_row) p.a_row += s0;
@@ -169,8 +185,9 @@ __global__ void __launch_bounds__(kLinThreads) linear_mma_kernel(const LinArgs<b
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   griddep_wait();
   LinArgs<bf16> p = p_in;
-  if (!lin_enter_group(p, kLinBM)) return;
-  const int row0 = blockIdx.y * kLinBM, col0 = blockIdx.x * kLinBN;
+  int row_tile;
+  if (!lin_enter_group(p, kLinBM, row_tile)) return;
+  const int row0 = row_tile * kLinBM, col0 = blockIdx.x * kLinBN;
   const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
   const bool vec_a = (p.lda % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.a) & 15) == 0);
   const bool vec_w = (p.k % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.w) & 15) == 0);
@@ -239,8 +256,9 @@ __global__ void __launch_bounds__(kLinF32Threads) linear_f32_kernel(const LinArg
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   griddep_wait();
   LinArgs<float> p = p_in;
-  if (!lin_enter_group(p, 64)) return;
-  const int row0 = blockIdx.y * 64, col0 = blockIdx.x * 64;
+  int row_tile;
+  if (!lin_enter_group(p, 64, row_tile)) return;
+  const int row0 = row_tile * 64, col0 = blockIdx.x * 64;
   float acc[4][4];
 #pragma unroll
   for (int i = 0; i < 4; ++i)

@@ -1,5 +1,6 @@
 // Routing of a mixture of experts for a ragged batch (the experts' matrix products are the grouped mode of linear_any.cuh).
 //
+//   moe_router_kernel   per row: the router's logits, fp32 accumulation
 //   moe_route_kernel    per row: s = sigmoid(logits) (or, softmax set, the softmax over all experts); choice = s + correction; the experts of all but the keep_groups best groups
 //                       (a group's score = the sum of its two largest choice scores) are barred; the `top` largest remaining choice
 //                       scores are chosen (the lower index wins a tie); weights = s of the chosen / (their sum + 1e-20), or, plain set, s of the
@@ -13,6 +14,27 @@
 #include "layer_ops.cuh"
 
 namespace mtx {
+
+// logits[r, e] = <x[r, :], w[e, :]> with fp32 accumulation: one CTA per row, a warp per expert in turn (few experts, so a tile of
+// a matrix-product kernel would be mostly padding and its k loop one long chain)
+template <typename T>
+__global__ void __launch_bounds__(256) moe_router_kernel(const T* x, const T* w, float* logits, int experts, int width) {
+  griddep_wait();
+  const int r = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const T* xr = x + size_t(r) * width;
+  for (int e = warp; e < experts; e += 8) {
+    const T* we = w + size_t(e) * width;
+    float acc0 = 0.0f, acc1 = 0.0f;
+    int c = lane * 2;
+    for (; c + 1 < width; c += 64) {
+      acc0 = fmaf(act_f32(xr[c]), act_f32(we[c]), acc0);
+      acc1 = fmaf(act_f32(xr[c + 1]), act_f32(we[c + 1]), acc1);
+    }
+    if (c < width) acc0 = fmaf(act_f32(xr[c]), act_f32(we[c]), acc0);
+    const float sum = warp_sum(acc0 + acc1);
+    if (lane == 0) logits[size_t(r) * experts + e] = sum;
+  }
+}
 
 struct MoeRouteArgs {
   const float* logits;      // [rows, experts]

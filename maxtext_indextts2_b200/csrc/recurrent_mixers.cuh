@@ -19,6 +19,7 @@
 //
 //   recurrent_prepare_kernel   per row: the GLA's decays (low-rank up-projection, bias, sigmoid^(1/tau)) or the mLSTM's two log gates
 //   delta_prepare_kernel       per row: the delta rule's decays, unit keys and removal vectors a u
+//   lowrank_split_kernel       the inputs of the gated delta rule's low-rank decay and gate projections in the matmul dtype
 //   gdelta_prepare_kernel      per row: the gated delta rule's convolutions, silu, unit vectors, decays and write strengths
 //   recurrent_scan_kernel      the walk
 //   recurrent_out_kernel<T>    per row and head: o / rms(o) * weight * gate(g) * out_scale -> the activation of the output projection
@@ -130,87 +131,111 @@ __host__ __device__ inline GDeltaCols gdelta_cols(int heads, int kv_heads, int d
 template <typename T>
 struct GDeltaPrepareArgs {
   const float* proj;     // [rows, ld]: q | k | v (C = 2 * kv_heads * dim + heads * vdim columns from column 0), then beta at b_col (heads),
-  long long ld;          // the decay's input at a_col (heads, or rank), the low-rank gate's input at g_col (gate_rank)
-  int b_col, a_col, g_col;
-  int heads, kv_heads, dim, vdim, taps, rank, gate_rank;
+  long long ld;          // and, rank == 0, the decay's input at a_col (heads)
+  int b_col, a_col;
+  int heads, kv_heads, dim, vdim, taps, rank;
   float key_eps;
   const float* conv_w;   // [taps, C]
   const float* state;    // [slots, taps - 1, C]: the projection row of position p at p % (taps - 1)
   const float* a_log;    // [heads]
   const float* bias;     // rank == 0: [heads]; else [heads * dim]
-  const float* up_t;     // [rank, heads * dim] (rank > 0)
+  const float* z;        // rank > 0: [rows, heads * dim] the decay's low-rank projection (before the bias)
   const int* group;
   const int* pos;
   float* out;            // [rows, gdelta_cols().n]
-  T* gate_low;           // [rows, gate_rank] the low-rank gate's input in the matmul dtype (gate_rank > 0)
 };
 
 __device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.0f) + log1pf(expf(-fabsf(z))); }
 
-// one CTA per row; dynamic shared memory: C + rank floats.  The row `back` steps before row r is row r - back of the batch when that
-// is the same sequence's previous position, a row of the state when the run began later, and zero before the sequence's start.
+// The inputs of the low-rank projections in the matmul dtype: the decay's (proj columns [a_col, a_col + rank)) as TWO parts side by
+// side, hi = the value rounded to the matmul dtype and lo = what the rounding left, so that a product with the up-projection
+// written twice along k sums to the fp32 value's product; the gate's (proj columns [g_col, g_col + gate_rank)) rounded once.
+template <typename T>
+__global__ void __launch_bounds__(256) lowrank_split_kernel(const float* proj, long long ld, int a_col, int rank, int g_col, int gate_rank, T* decay_in,
+                                                            T* gate_in, long long rows) {
+  griddep_wait();
+  const long long per = rank + gate_rank, total = rows * per;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / per;
+    const int e = int(i % per);
+    if (e < rank) {
+      const float v = proj[r * ld + a_col + e];
+      const T hi = to_act<T>(v);
+      decay_in[r * 2 * rank + e] = hi;
+      decay_in[r * 2 * rank + rank + e] = to_act<T>(v - act_f32(hi));
+    } else {
+      gate_in[r * gate_rank + (e - rank)] = to_act<T>(proj[r * ld + g_col + (e - rank)]);
+    }
+  }
+}
+
+// grid (rows, parts): the CTAs of a row share its units, a warp takes a unit at a time: a q or k head (convolution, silu, unit
+// vector), a v head (convolution, silu), a head's decays, or the write strengths.  The row `back` steps before row r is row r - back
+// of the batch when that is the same sequence's previous position, a row of the state when the run began later, and zero before
+// the sequence's start (up to kGdMaxBack earlier rows are located once per CTA).
+constexpr int kGdMaxBack = 16, kGdMaxPerLane = 8;  // (dim <= 32 * kGdMaxPerLane)
+
 template <typename T>
 __global__ void __launch_bounds__(256) gdelta_prepare_kernel(const GDeltaPrepareArgs<T> a) {
-  extern __shared__ float s_gd[];
-  constexpr int kMaxBack = 16;
-  __shared__ const float* s_src[kMaxBack];
+  __shared__ const float* s_src[kGdMaxBack];
   griddep_wait();
   const int r = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
   const int H = a.heads, G = a.kv_heads, d = a.dim, dv = a.vdim, C = 2 * G * d + H * dv, ring = a.taps - 1;
-  float* buf = s_gd;        // [C] silu(conv(.))
-  float* low = s_gd + C;    // [rank]
   const int p = a.pos[r], grp = a.group[r];
   const int n_back = ring < p ? ring : p;
   const float* row = a.proj + size_t(r) * a.ld;
-  if (tid < n_back && tid < kMaxBack) {
-    const int back = tid + 1, rr = r - back;
+  auto source = [&](int back) {
+    const int rr = r - back;
     const bool in_batch = rr >= 0 && a.group[rr] == grp && a.pos[rr] == p - back;
-    s_src[tid] = in_batch ? a.proj + size_t(rr) * a.ld : a.state + (size_t(grp) * ring + (p - back) % ring) * C;
-  }
-  for (int e = tid; e < a.rank; e += blockDim.x) low[e] = row[a.a_col + e];
+    return in_batch ? a.proj + size_t(rr) * a.ld : a.state + (size_t(grp) * ring + (p - back) % ring) * C;
+  };
+  if (tid < n_back && tid < kGdMaxBack) s_src[tid] = source(tid + 1);
   __syncthreads();
-  for (int c = tid; c < C; c += blockDim.x) {
+  auto conv_silu = [&](int c) {
     float y = row[c] * a.conv_w[size_t(ring) * C + c];
     for (int back = 1; back <= n_back; ++back) {
-      const float* src;
-      if (back <= kMaxBack) {
-        src = s_src[back - 1];
-      } else {
-        const int rr = r - back;
-        const bool in_batch = rr >= 0 && a.group[rr] == grp && a.pos[rr] == p - back;
-        src = in_batch ? a.proj + size_t(rr) * a.ld : a.state + (size_t(grp) * ring + (p - back) % ring) * C;
-      }
+      const float* src = back <= kGdMaxBack ? s_src[back - 1] : source(back);
       y = fmaf(src[c], a.conv_w[size_t(ring - back) * C + c], y);
     }
-    buf[c] = y / (1.0f + expf(-y));
-  }
-  __syncthreads();
+    return y / (1.0f + expf(-y));
+  };
   const GDeltaCols cc = gdelta_cols(H, G, d, dv);
   float* out = a.out + size_t(r) * cc.n;
-  for (int u = warp; u < 2 * G; u += nw) {  // unit vectors: the q heads, then the k heads
-    const float* src = buf + u * d;
-    float ss = 0.0f;
-    for (int c = lane; c < d; c += 32) ss = fmaf(src[c], src[c], ss);
-    ss = warp_sum(ss);
-    const float inv = 1.0f / sqrtf(ss + a.key_eps);
-    float* dst = out + (u < G ? cc.q + u * d : cc.k + (u - G) * d);
-    for (int c = lane; c < d; c += 32) dst[c] = src[c] * inv;
-  }
-  for (int c = tid; c < H * dv; c += blockDim.x) out[cc.v + c] = buf[2 * G * d + c];
-  for (int c = tid; c < H * d; c += blockDim.x) {
-    const int h = c / d;
-    float z;
-    if (a.rank > 0) {
-      z = a.bias[c];
-      for (int e = 0; e < a.rank; ++e) z = fmaf(a.up_t[size_t(e) * H * d + c], low[e], z);
-    } else {
-      z = row[a.a_col + h] + a.bias[h];
+  const int n_units = 2 * G + 2 * H + 1;
+  for (int u = blockIdx.y * nw + warp; u < n_units; u += gridDim.y * nw) {
+    if (u < 2 * G) {  // a q head, or a k head: unit vectors
+      float v[kGdMaxPerLane];
+      float ss = 0.0f;
+#pragma unroll
+      for (int i = 0; i < kGdMaxPerLane; ++i) {
+        const int c = lane + 32 * i;
+        v[i] = c < d ? conv_silu(u * d + c) : 0.0f;
+        ss = fmaf(v[i], v[i], ss);
+      }
+      ss = warp_sum(ss);
+      const float inv = 1.0f / sqrtf(ss + a.key_eps);
+      float* dst = out + (u < G ? cc.q + u * d : cc.k + (u - G) * d);
+#pragma unroll
+      for (int i = 0; i < kGdMaxPerLane; ++i) {
+        const int c = lane + 32 * i;
+        if (c < d) dst[c] = v[i] * inv;
+      }
+    } else if (u < 2 * G + H) {  // a v head
+      const int h = u - 2 * G;
+      for (int c = lane; c < dv; c += 32) out[cc.v + h * dv + c] = conv_silu(2 * G * d + h * dv + c);
+    } else if (u < 2 * G + 2 * H) {  // a head's decays
+      const int h = u - 2 * G - H;
+      const float rate = expf(a.a_log[h]);
+      if (a.rank > 0) {
+        for (int c = lane; c < d; c += 32) out[cc.decay + h * d + c] = expf(-rate * softplus_f(a.z[size_t(r) * H * d + h * d + c] + a.bias[h * d + c]));
+      } else {
+        const float g = expf(-rate * softplus_f(row[a.a_col + h] + a.bias[h]));
+        for (int c = lane; c < d; c += 32) out[cc.decay + h * d + c] = g;
+      }
+    } else {  // the write strengths
+      for (int h = lane; h < H; h += 32) out[cc.beta + h] = 1.0f / (1.0f + expf(-row[a.b_col + h]));
     }
-    out[cc.decay + c] = expf(-expf(a.a_log[h]) * softplus_f(z));
   }
-  for (int h = tid; h < H; h += blockDim.x) out[cc.beta + h] = 1.0f / (1.0f + expf(-row[a.b_col + h]));
-  if (a.gate_low)
-    for (int e = tid; e < a.gate_rank; e += blockDim.x) a.gate_low[size_t(r) * a.gate_rank + e] = to_act<T>(row[a.g_col + e]);
 }
 
 struct RecScanArgs {

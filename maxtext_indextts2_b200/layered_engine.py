@@ -40,7 +40,7 @@ _ATTN_VECS = ("q_norm", "k_norm", "slopes", "sink")
 _LATENT_MATS = ("w_uq", "w_uk_t", "w_uv")
 _LATENT_VECS = ("q_norm", "kv_norm", "sink")
 _REC_VECS = ("decay_up_t", "decay_bias", "gate_bias", "out_norm", "conv_w", "a_log")
-_REC_MATS = ("w_gate_up",)
+_REC_MATS = ("w_gate_up", "decay_up2")
 _SIDE_MATS = ("gate", "proj")
 _SIDE_VECS = ("norm",)
 _MOE_MATS = ("w_router", "w_gate_up", "w_down", "shared_gate_up", "shared_down")
@@ -306,6 +306,7 @@ class LayeredEngine(MaxEngine):
             d.rec.kv_heads, d.rec.conv_taps, d.rec.gate_rank = int(r["kv_heads"]), int(r["conv_taps"]), int(r.get("gate_rank", 0))
             for k in ("conv_w", "a_log", "w_gate_up"):
               setattr(d.rec, k, ptr(r.get(k)))
+            d.rec.decay_up_t = ptr(r.get("decay_up2"))  # (in the matmul dtype, written twice along its inputs)
             if d.rec.conv_taps > 1:  # the ring of a sequence's last projection rows (q | k | v before the convolution), per state slot
               states += (torch.zeros(slots, d.rec.conv_taps - 1, 2 * int(r["kv_heads"]) * dk + H * dv, dtype=f32, device=dev),)
               d.rec.conv_state = states[-1].data_ptr()

@@ -163,11 +163,13 @@ def layer_plan(config, tensors: Dict[str, torch.Tensor], i: int) -> Dict[str, An
     rec = dict(kind="gdelta", heads=H, kv_heads=G, dim=d, vdim=dv, decay_rank=0, gate_rank=0, gate_silu=1, q_scale=d**-0.5, tau=1.0, gate_cap=0.0,
                denom_eps=0.0, out_scale=1.0, key_eps=UNIT_EPS, conv_taps=taps, conv_w=_taps_major(conv),
                a_log=_shape(f32(p + "A_log"), (H,), p + "A_log"), out_norm=_shape(f32(p + "norm"), (dv,), p + "norm").repeat(H),
-               decay_up_t=None, w_gate_up=None)
+               decay_up2=None, w_gate_up=None)
     if per_channel:
       ra, rg = int(t[p + "a1"].shape[0]), int(t[p + "g1"].shape[0])
       rows += [_shape(t[p + "a1"], (ra, E), p + "a1"), _shape(t[p + "g1"], (rg, E), p + "g1")]
-      rec.update(decay_rank=ra, gate_rank=rg, gate_silu=0, decay_up_t=_shape(f32(p + "a2"), (H * d, ra), p + "a2").t().contiguous(),
+      a2 = _shape(t[p + "a2"], (H * d, ra), p + "a2")
+      # (the up-projection twice along its inputs: the device feeds it the fp32 input split into two parts of the matmul dtype)
+      rec.update(decay_rank=ra, gate_rank=rg, gate_silu=0, decay_up2=torch.cat([a2, a2], dim=1).contiguous(),
                  decay_bias=_shape(f32(p + "dt_bias"), (H * d,), p + "dt_bias"), w_gate_up=_shape(t[p + "g2"], (H * dv, rg), p + "g2"))
     else:
       rows += [_shape(t[p + "a"], (H, E), p + "a"), _shape(t[p + "g"], (H * dv, E), p + "g")]

@@ -61,7 +61,7 @@ def test_model_folder_round_trip_and_plan(tmp_path):
   # per-channel decays and the sigmoid gate come through low ranks that the tensors' shapes give
   c = p3["rec"]
   assert p3["n_in"] == 8 + 8 + 12 + 2 + 5 + 6 and (c["decay_rank"], c["gate_rank"], c["gate_silu"], c["conv_taps"]) == (5, 6, 0, 5)
-  assert torch.equal(c["decay_up_t"], tensors["l3.mix.a2"].float().t()) and c["w_gate_up"].shape == (12, 6) and c["decay_bias"].shape == (16,)
+  assert torch.equal(c["decay_up2"], torch.cat([tensors["l3.mix.a2"]] * 2, dim=1)) and c["w_gate_up"].shape == (12, 6) and c["decay_bias"].shape == (16,)
   # experts: gate and up rows interleaved, stacked; softmax scores used as they are
   m = p0["moe"]
   assert (m["experts"], m["top"], m["ff"], m["shared_ff"], m["score_softmax"], m["plain_weights"], m["act_silu"]) == (5, 2, 14, 10, 1, 1, 1)
