@@ -262,9 +262,20 @@ __device__ __forceinline__ int smax_blocks_seen(int i, int window, int pool) {
   return (pool > 0 && past > 0) ? past / pool : 0;
 }
 
-// cap * tanh(s / cap) by one exponential and one division: absolute error of a few 1e-7 * cap
-__device__ __forceinline__ float smax_softcap_fast(float s, float cap) {
-  return cap * (1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * s / cap)));
+__device__ __forceinline__ float smax_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float smax_rcp(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// cap * tanh(raw * scale / cap) = cap - 2 cap / (1 + 2^(raw * mul)) with mul = scale * 2 log2(e) / cap: one multiplication, two
+// special-function instructions and a fused multiply-add per score; absolute error of a few 1e-7 * cap
+__device__ __forceinline__ float smax_softcap_scaled(float raw, float mul, float cap) {
+  return fmaf(-2.0f * cap, smax_rcp(1.0f + smax_ex2(raw * mul)), cap);
 }
 
 __device__ __forceinline__ float smax_gate(const float* gate, long long ld, int row, int h) {
@@ -496,6 +507,9 @@ __global__ void __launch_bounds__(128) softmax_attention_mma_kernel(const Softma
   const float slope = a.slopes ? a.slopes[h] : 0.0f;
   const int pi0 = p0 + g, pi1 = p0 + g + 8;
   const int nb0 = smax_blocks_seen(pi0, a.window, a.pool), nb1 = smax_blocks_seen(pi1, a.window, a.pool);
+  const int nb_first = smax_blocks_seen(p0, a.window, a.pool);
+  const bool capped = a.softcap > 0.0f, sloped = a.slopes != nullptr;
+  const float cap_mul = capped ? a.scale * 2.8853900817779268f / a.softcap : 0.0f;
 
   if (n_key_tiles > 0) load_tile(0, 0);
   for (int it = 0; it < n_key_tiles; ++it) {
@@ -512,6 +526,8 @@ __global__ void __launch_bounds__(128) softmax_attention_mma_kernel(const Softma
       const int gt = tile_lo + it;
       const bool pooled = gt < pool_tiles;
       const int j0 = pooled ? gt * KT : lo + (gt - pool_tiles) * KT;
+      // a tile whose every key every row of the query tile sees (most tiles of a long window) needs no masks
+      const bool every_key_seen = pooled ? j0 + KT <= nb_first : (j0 + KT - 1 <= p0 && (a.window <= 0 || p_last - j0 < a.window));
       float s[KT / 8][4];
 #pragma unroll
       for (int nb = 0; nb < KT / 8; ++nb) {
@@ -527,11 +543,14 @@ __global__ void __launch_bounds__(128) softmax_attention_mma_kernel(const Softma
       for (int nb = 0; nb < KT / 8; ++nb) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const int j = j0 + nb * 8 + 2 * t + (e & 1), pi = (e & 2) ? pi1 : pi0;
-          const bool seen = pooled ? j < ((e & 2) ? nb1 : nb0) : (j <= pi && (a.window <= 0 || pi - j < a.window));
-          float sc = s[nb][e] * a.scale;
-          if (a.softcap > 0.0f) sc = smax_softcap_fast(sc, a.softcap);
-          s[nb][e] = seen ? (pooled ? sc : sc - slope * float(pi - j)) : -INFINITY;
+          float sc = capped ? smax_softcap_scaled(s[nb][e], cap_mul, a.softcap) : s[nb][e] * a.scale;
+          if (!every_key_seen || (sloped && !pooled)) {
+            const int j = j0 + nb * 8 + 2 * t + (e & 1), pi = (e & 2) ? pi1 : pi0;
+            const bool seen = pooled ? j < ((e & 2) ? nb1 : nb0) : (j <= pi && (a.window <= 0 || pi - j < a.window));
+            if (sloped && !pooled) sc -= slope * float(pi - j);
+            sc = seen ? sc : -INFINITY;
+          }
+          s[nb][e] = sc;
         }
         mx0 = fmaxf(mx0, fmaxf(s[nb][0], s[nb][1]));
         mx1 = fmaxf(mx1, fmaxf(s[nb][2], s[nb][3]));
@@ -704,6 +723,7 @@ __global__ void __launch_bounds__(kSdecWarps * 32) softmax_attention_decode_kern
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[mb][e] = 0.0f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};  // heads 2t, 2t + 1
+  const float cap_mul = a.softcap > 0.0f ? a.scale * 2.8853900817779268f / a.softcap : 0.0f;
   float slope0 = 0.0f, slope1 = 0.0f;
   if (a.slopes) {
     slope0 = 2 * t < rep ? a.slopes[head0 + 2 * t] : 0.0f;
@@ -745,10 +765,7 @@ __global__ void __launch_bounds__(kSdecWarps * 32) softmax_attention_decode_kern
       const bool sa_ = pooled ? ja < nb : (ja <= pos && (a.window <= 0 || pos - ja < a.window));
       const bool sb_ = pooled ? jb < nb : (jb <= pos && (a.window <= 0 || pos - jb < a.window));
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        c[e] *= a.scale;
-        if (a.softcap > 0.0f) c[e] = smax_softcap_fast(c[e], a.softcap);
-      }
+      for (int e = 0; e < 4; ++e) c[e] = a.softcap > 0.0f ? smax_softcap_scaled(c[e], cap_mul, a.softcap) : c[e] * a.scale;
       const float da = pooled ? 0.0f : float(pos - ja), db = pooled ? 0.0f : float(pos - jb);
       c[0] = sa_ ? c[0] - slope0 * da : -INFINITY;
       c[1] = sa_ ? c[1] - slope1 * da : -INFINITY;
