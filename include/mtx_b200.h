@@ -569,6 +569,7 @@ typedef struct {
   const void* side_gate;   /* [side_dim, width] */
   const void* side_proj;   /* [width, side_dim] */
   const float* side_norm;  /* [width] */
+  int32_t side_gate_rows;  /* rows of side_gate: side_dim, or more with zero rows up to a tile edge of the tensor-core GEMM; 0 = side_dim */
 } mtx_layer_desc;
 
 typedef struct {

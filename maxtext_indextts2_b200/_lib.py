@@ -179,6 +179,7 @@ class LayerDesc(ctypes.Structure):
       + [(n, ctypes.c_void_p) for n in ("conv1", "conv2", "conv_state")]
       + [(n, ctypes.c_int32) for n in ("side_dim", "side_col")]
       + [(n, ctypes.c_void_p) for n in ("side_gate", "side_proj", "side_norm")]
+      + [("side_gate_rows", ctypes.c_int32)]
   )
 
 

@@ -1472,10 +1472,11 @@ int prenorm_layer(mtx_layered* e, int li, const mtx_ragged_batch& b, cudaStream_
   if (!has_side) return pre_norm_step<T>(e, e->y, nullptr, nullptr, false, li + 1, nullptr, b, st);  // x += the last sublayer; the next layer's norm
   // x += the last sublayer, and x in the matmul dtype for the side input's gate
   MTX_TRY(pre_norm_step<T>(e, e->y, nullptr, nullptr, true, c.num_layers, nullptr, b, st));
-  MTX_TRY((linear<T, LIN_PLAIN>(e, e->xb, l.side_gate, nullptr, e->qkv, nullptr, rows, l.side_dim, E, st)));
+  const int gate_rows = l.side_gate_rows > l.side_dim ? l.side_gate_rows : l.side_dim;
+  MTX_TRY((linear<T, LIN_PLAIN>(e, e->xb, l.side_gate, nullptr, e->qkv, nullptr, rows, gate_rows, E, st)));
   const long long total = (long long)rows * l.side_dim;
   const int blocks = int((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
-  MTX_TRY(launch(side_act_kernel<T>, dim3(blocks), dim3(256), 0, st, (const float*)e->qkv, (long long)l.side_dim, b.token, static_cast<const T*>(c.side_embed),
+  MTX_TRY(launch(side_act_kernel<T>, dim3(blocks), dim3(256), 0, st, (const float*)e->qkv, (long long)gate_rows, b.token, static_cast<const T*>(c.side_embed),
                  (long long)c.side_width, l.side_col, c.vocab, static_cast<T*>(e->act), l.side_dim, total));
   MTX_TRY((linear<T, LIN_PLAIN>(e, e->act, l.side_proj, nullptr, e->y, nullptr, rows, E, l.side_dim, st)));
   return pre_norm_step<T>(e, e->y, l.side_norm, nullptr, false, li + 1, nullptr, b, st);  // x += unit(y) * side_norm; the next layer's norm
@@ -1693,6 +1694,7 @@ int check_prenorm(mtx_layered* e, int i) {
       return fail(MTX_ERR_ARG, "layer %d: the side input's weights, table or columns are missing", i);
     if (l.side_dim > e->max_ff) e->max_ff = l.side_dim;
     if (l.side_dim > e->max_nqkv) e->max_nqkv = l.side_dim;
+    if (l.side_gate_rows > e->max_nqkv) e->max_nqkv = l.side_gate_rows;
   }
   e->prenorm = true;
   return MTX_OK;

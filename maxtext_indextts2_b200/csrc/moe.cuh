@@ -22,15 +22,31 @@ __global__ void __launch_bounds__(256) moe_router_kernel(const T* x, const T* w,
   griddep_wait();
   const int r = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const T* xr = x + size_t(r) * width;
+  // bf16 rows of whole 16-byte chunks: eight channels per load
+  const bool vec = sizeof(T) == 2 && width % 8 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) == 0;
   for (int e = warp; e < experts; e += 8) {
     const T* we = w + size_t(e) * width;
     float acc0 = 0.0f, acc1 = 0.0f;
-    int c = lane * 2;
-    for (; c + 1 < width; c += 64) {
-      acc0 = fmaf(act_f32(xr[c]), act_f32(we[c]), acc0);
-      acc1 = fmaf(act_f32(xr[c + 1]), act_f32(we[c + 1]), acc1);
+    if (vec) {
+      for (int c = lane * 8; c < width; c += 256) {
+        const uint4 xv = *reinterpret_cast<const uint4*>(xr + c), wv = *reinterpret_cast<const uint4*>(we + c);
+        const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+        const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 xf = __bfloat1622float2(xp[i]), wf = __bfloat1622float2(wp[i]);
+          acc0 = fmaf(xf.x, wf.x, acc0);
+          acc1 = fmaf(xf.y, wf.y, acc1);
+        }
+      }
+    } else {
+      int c = lane * 2;
+      for (; c + 1 < width; c += 64) {
+        acc0 = fmaf(act_f32(xr[c]), act_f32(we[c]), acc0);
+        acc1 = fmaf(act_f32(xr[c + 1]), act_f32(we[c + 1]), acc1);
+      }
+      if (c < width) acc0 = fmaf(act_f32(xr[c]), act_f32(we[c]), acc0);
     }
-    if (c < width) acc0 = fmaf(act_f32(xr[c]), act_f32(we[c]), acc0);
     const float sum = warp_sum(acc0 + acc1);
     if (lane == 0) logits[size_t(r) * experts + e] = sum;
   }

@@ -328,6 +328,7 @@ class LayeredEngine(MaxEngine):
         if sd:
           d.side_dim, d.side_col = int(sd["dim"]), int(sd["col"])
           d.side_gate, d.side_proj, d.side_norm = ptr(sd["gate"]), ptr(sd["proj"]), ptr(sd["norm"])
+          d.side_gate_rows = int(sd["gate"].shape[0])
       for k in ("wo", "w_gate_up", "w_down"):
         setattr(d, k, ptr(l.get(k)))
       self._states.append(states)

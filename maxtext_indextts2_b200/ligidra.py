@@ -201,7 +201,11 @@ def layer_plan(config, tensors: Dict[str, torch.Tensor], i: int) -> Dict[str, An
   sd = int(config.token_side_dim)
   if sd:
     s = f"l{i}.side."
-    plan["side"] = dict(dim=sd, col=i * sd, gate=_shape(t[s + "gate"], (sd, E), s + "gate"), proj=_shape(t[s + "proj"], (E, sd), s + "proj"),
+    gate = _shape(t[s + "gate"], (sd, E), s + "gate")
+    pad = (-sd) % TILE_ROWS
+    if pad and E % 64 == 0:  # zero rows up to a whole tile of the tensor-core GEMM
+      gate = torch.cat([gate, torch.zeros(pad, E, dtype=gate.dtype, device=dev)], dim=0)
+    plan["side"] = dict(dim=sd, col=i * sd, gate=gate, proj=_shape(t[s + "proj"], (E, sd), s + "proj"),
                         norm=_shape(f32(s + "norm"), (E,), s + "norm"))
   return plan
 

@@ -86,6 +86,10 @@ def test_input_projection_is_padded_to_whole_tiles_when_the_width_allows():
   plan = lg.model_plan(config, t)["layers"][0]
   n = 8 + 8 + 16 + 2 + 2 + 16
   assert plan["n_in"] == 128 and float(plan["w_in"][n:].float().abs().max()) == 0.0 and plan.get("side") is None
+  cfg = lg.model_dict(64, 50, [lg.delta_layer(2, 1, 8, 8)], side_dim=5)
+  config = pyconfig.from_model_dict(cfg, **KW)
+  side = lg.model_plan(config, lg.random_tensors(config, seed=0))["layers"][0]["side"]
+  assert side["gate"].shape == (128, 64) and float(side["gate"][5:].float().abs().max()) == 0.0 and side["proj"].shape == (64, 5)
 
 
 @pytest.mark.parametrize("break_it,match", [
