@@ -268,9 +268,17 @@ __global__ void __launch_bounds__(256) group_norm_step_kernel(const float* y, fl
 
 template <typename T>
 __global__ void __launch_bounds__(256) group_norm_rows_kernel(const float* x, const int* rows, const float* w, float eps, T* out, int width, int groups) {
+  __shared__ float red[8];
   griddep_wait();
   const int src = rows ? rows[blockIdx.x] : int(blockIdx.x), warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gs = width / groups;
   const float* xr = x + size_t(src) * width;
+  if (groups == 1) {  // a plain RMS norm: the whole CTA on the one group
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) ss = fmaf(xr[c], xr[c], ss);
+    const float f = 1.0f / sqrtf(block_sum(ss, red) / float(width) + eps);
+    for (int c = threadIdx.x; c < width; c += blockDim.x) out[size_t(blockIdx.x) * width + c] = to_act<T>(xr[c] * f * w[c]);
+    return;
+  }
   for (int g = warp; g < groups; g += 8) {  // (only the rows whose logits are wanted come here: a warp per group is enough)
     const int base = g * gs;
     float ss = 0.0f;

@@ -104,22 +104,24 @@ def pooled_window_attention(q, k, v, scale, cap, window, pool, sink, hooks=None)
   "no_sink": True} make a deliberate fault."""
   T, H, d = q.shape
   G, dv = k.shape[1], v.shape[2]
-  rep = H // G
+  head_of = np.arange(H) // (H // G)  # the key head of every query head
   hooks = hooks or {}
   out = np.zeros((T, H, dv))
   for i in range(T):
     toks, blocks = visible(i, window + hooks.get("window", 0) if window else 0, pool)
     if hooks.get("blocks"):
       blocks = list(range(max(0, len(blocks) + hooks["blocks"])))
-    for h in range(H):
-      g = h // rep
-      keys = [k[j, g] for j in toks] + [k[b * pool : (b + 1) * pool, g].mean(axis=0) for b in blocks]
-      vals = [v[j, g] for j in toks] + [v[b * pool : (b + 1) * pool, g].mean(axis=0) for b in blocks]
-      s = soft_cap(np.array([q[i, h] @ kk for kk in keys]) * scale, cap)
-      m = max(s.max(), sink[h]) if sink is not None else s.max()
-      p = np.exp(s - m)
-      denom = p.sum() + (math.exp(sink[h] - m) if (sink is not None and not hooks.get("no_sink")) else 0.0)
-      out[i, h] = (p[:, None] * np.array(vals)).sum(axis=0) / denom
+    keys = np.stack([k[j] for j in toks] + [k[b * pool : (b + 1) * pool].mean(axis=0) for b in blocks])  # [n, G, d]
+    vals = np.stack([v[j] for j in toks] + [v[b * pool : (b + 1) * pool].mean(axis=0) for b in blocks])  # [n, G, dv]
+    s = soft_cap(np.einsum("hd,nhd->hn", q[i], keys[:, head_of]) * scale, cap)                           # [H, n]
+    m = s.max(axis=1)
+    if sink is not None:
+      m = np.maximum(m, sink)
+    p = np.exp(s - m[:, None])
+    denom = p.sum(axis=1)
+    if sink is not None and not hooks.get("no_sink"):
+      denom = denom + np.exp(sink - m)
+    out[i] = np.einsum("hn,nhc->hc", p, vals[:, head_of]) / denom[:, None]
   return out
 
 
