@@ -1,7 +1,7 @@
 // The layered engine of include/mtx_b200.h (mtx_layered_*): a decoder given as a list of layer descriptors, stepped over ragged
 // batches whose keys and values live in page pools.  Host code only: the kernels are in linear_any.cuh (any-shape projections, also
 // grouped by expert), gemm_rows.cuh (the tcgen05 projections, for shapes made of whole 128 x 64 tiles), layer_ops.cuh (norms,
-// residual, cache append), window_attention*.cuh (the sigmoid window mixer), softmax_attention.cuh (causal softmax attention with
+// residual, cache append), grouped_gemm.cuh (the experts' products of steps with many rows), window_attention*.cuh (the sigmoid window mixer), softmax_attention.cuh (causal softmax attention with
 // rotary positions), recurrent_mixers.cuh (GLA, mLSTM and the delta rule over state slots), latent_attention.cuh (attention through
 // cached latents) and moe.cuh (routing).
 #include <cmath>
@@ -12,6 +12,7 @@
 #include "../../include/mtx_b200.h"
 #include "layer_ops.cuh"
 #include "linear_any.cuh"
+#include "grouped_gemm.cuh"
 #include "window_attention.cuh"
 #include "window_attention_mma.cuh"
 #include "window_attention_decode.cuh"
@@ -267,6 +268,21 @@ int linear_grouped(const void* a, const int* a_row, const void* w, long long w_s
   // range of y per group
   const bool packed = groups <= 64;
   p.groups = packed ? groups : 0;
+  if constexpr (sizeof(T) == 2) {
+    // many rows per group (a prompt portion): 128-row tiles behind a three-stage cp.async ring (grouped_gemm.cuh); 2 forces it
+    // whenever the shape allows, 0 switches it off
+    static const int pipe = env_int("MTX_GROUPED_PIPE", 1);
+    const bool shape_ok = packed && k % kGgBK == 0 && (reinterpret_cast<uintptr_t>(a) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (w_stride % 8) == 0;
+    if (shape_ok && (pipe == 2 || (pipe == 1 && slots >= kGgBM * groups))) {
+      static bool attr_set = false;  // per instantiation
+      if (!attr_set) {
+        MTX_CUDA(cudaFuncSetAttribute(grouped_mma_pipe_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kGgSmemBytes)));
+        attr_set = true;
+      }
+      const dim3 pgrid((n + kGgBN - 1) / kGgBN, (slots + kGgBM - 1) / kGgBM + groups, 1);
+      return launch(grouped_mma_pipe_kernel<EPI>, pgrid, dim3(kGgThreads), kGgSmemBytes, st, p);
+    }
+  }
   const dim3 grid((n + 63) / 64, packed ? (slots + 63) / 64 + groups : (slots + 63) / 64, packed ? 1 : groups);
   if constexpr (sizeof(T) == 4) return launch(linear_f32_kernel<EPI>, grid, dim3(kLinF32Threads), 0, st, p);
   else return launch(linear_mma_kernel<EPI>, grid, dim3(kLinThreads), 0, st, p);

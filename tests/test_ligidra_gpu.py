@@ -432,6 +432,18 @@ def test_sizes_made_of_whole_tensor_core_tiles_on_a_bfloat16_engine():
   assert rms_err(in_portions(engine, toks, [70], decode=20), want) < LOOSE
 
 
+def test_many_rows_per_expert_take_the_pipelined_grouped_products():
+  """A prompt portion with at least 128 (row, choice) slots per expert runs its experts on 128-row tiles behind a cp.async ring;
+  experts with unequal and odd row counts, a last column tile that is not whole, then single tokens on the small-tile kernel."""
+  cfg = model([dlt(moe(3, 2, 72, 0), heads=2, kv_heads=1, dim=32, vdim=32), att(moe(2, 2, 64, 64), heads=2, kv_heads=1, dim=32, vdim=32)], width=128, vocab=200, side_dim=0)
+  toks = tokens_for(cfg, 333)
+  t = weights(cfg, 25, toks)
+  want = ref.forward(cfg, t, toks)
+  engine = make_engine(cfg, t, dtype="bfloat16", tokens_per_page=64, num_pages=14, max_len=400)
+  assert rms_err(whole(engine, toks), want) < LOOSE
+  assert rms_err(in_portions(engine, toks, [301, 2, 27], decode=3), want) < LOOSE
+
+
 # ---- the tensor-core attention with pooled blocks, cap and sink (bf16, head sizes in multiples of 16) --------------------------------
 
 @pytest.mark.parametrize("heads,kv_heads,dim,page,window,pool", [(4, 2, 64, 16, 70, 8), (2, 2, 16, 8, 33, 3), (8, 1, 32, 64, 20, 1), (6, 2, 48, 4, 64, 5),
